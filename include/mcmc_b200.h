@@ -1,0 +1,235 @@
+/*
+ * mcmc_b200 — C-ABI of the B200 (sm_100a) HMC hot path for the two-layer
+ * Bayesian MLP of NVIDIA/mcmc-bnn-example.
+ *
+ * The reference has no FFI layer: its boundary is the C++ header API under
+ * include/mcmc/ (mcmc_step, log_acpt_prec, main_loop, Network, DeviceMatrix).
+ * Every entry point below names the reference interface it stands in for
+ * (paths inside the reference project).  All functions return an
+ * MCMC_B200_* status; nothing aborts the process (the reference aborts in
+ * include/mcmc/utils_cuda.h:30-46).  Plain pointers and sizes only.
+ *
+ * Conventions shared with the reference:
+ *   - parameter vector of P = D*H + 2H + 1 floats: W0[k][j] at k*H + j, b0 at
+ *     D*H, W1 at D*H + H, b1 at D*H + 2H (mcmc_step_ffma.h:35-44, :244);
+ *   - X is row-major [N][D] FP32, y is [N] FP32;
+ *   - "loss" is a log-density that is maximised, gradients are d(log p)/dw,
+ *     the momentum update is m += eps * grad (mcmc_step_ffma.h:106-120).
+ *
+ * One host thread per context at a time.  Contexts are independent.
+ */
+#ifndef MCMC_B200_H_
+#define MCMC_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MCMC_B200_OK 0
+#define MCMC_B200_ERR_INVALID 1      /* bad argument or call order */
+#define MCMC_B200_ERR_CUDA 2         /* a CUDA runtime/driver call failed */
+#define MCMC_B200_ERR_NOMEM 3
+#define MCMC_B200_ERR_TIMEOUT 4      /* a bounded device-side wait ran out */
+#define MCMC_B200_ERR_NCCL 5
+#define MCMC_B200_ERR_UNSUPPORTED 6  /* shape / mode not built */
+
+#define MCMC_B200_LIK_STUDENT_T 0    /* global_params.h:39-45 */
+#define MCMC_B200_LIK_GAUSSIAN 1
+
+#define MCMC_B200_PREC_FP32 0        /* FFMA path; stands in for mcmc_step_ffma.h */
+#define MCMC_B200_PREC_TF32 1        /* tcgen05 kind::tf32 path; stands in for mcmc_step_tc.h */
+
+/* Everything the reference fixes at compile time in global_params.h:27-58. */
+typedef struct mcmc_b200_config {
+  int32_t D;               /* input features; 22 */
+  int32_t H;               /* hidden units; 40 (or 128) */
+  int32_t likelihood;      /* MCMC_B200_LIK_* */
+  int32_t precision;       /* MCMC_B200_PREC_* */
+  double lik_scale;        /* Student-t scale (100) or Gaussian sigma */
+  double lik_df;           /* Student-t degrees of freedom (2.2) */
+  double prior_scale;      /* sigma of the N(0, s^2) prior (200) */
+  int32_t leapfrog_steps;  /* LEAPFROG_STEPS (1000) */
+  int32_t burn_in;         /* BURN_IN_STEPS (100): iterations whose state is not stored */
+  int32_t adapt_steps;     /* STEP_SIZE_ADAPT_STEPS (100) */
+  int32_t sample_capacity; /* stored samples per window (SAMPLE_STEPS, 800); 0 = store none */
+  double eps0;             /* STEP_SIZE_INIT (0.01) */
+  double target_rate;      /* STEP_SIZE_TARGET_RATE (0.2) */
+  double decrement;        /* STEP_SIZE_DECREMENT (0.1) */
+  double increment;        /* STEP_SIZE_INCREMENT (0.01) */
+  uint64_t seed;           /* SEED_INIT; keys the Philox streams */
+  int32_t trace_iters;     /* first K iterations whose draws and energies are recorded */
+  int32_t slices;          /* CTAs per window per launch; 0 = chosen from the SM count */
+} mcmc_b200_config;
+
+/* Fills a config with the reference's shipped preset (global_params.h:27-58)
+ * or with the Gaussian/N(0,1)/L=10/eps=1e-3 benchmark preset. */
+void mcmc_b200_config_reference(mcmc_b200_config* cfg);
+void mcmc_b200_config_baseline(mcmc_b200_config* cfg);
+
+typedef struct mcmc_b200_ctx mcmc_b200_ctx;
+
+/* Library-wide: last error text of the calling thread (also set by failed
+ * create calls, where no context exists yet). */
+const char* mcmc_b200_last_error(void);
+/* 1 when the library was built with the tcgen05 kernels for sm_100a. */
+int mcmc_b200_has_tf32(void);
+
+/*
+ * Context = the reference's per-process state (main.h:153-183: data, labels,
+ * Network, loss buffers, prev_step_*, final_samples) for `n_windows`
+ * independent windows of `rows` rows each, on CUDA device `device`.
+ * Stands in for the allocations of main_loop (main.h:117-185).
+ */
+int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows, int64_t rows,
+                     mcmc_b200_ctx** out);
+void mcmc_b200_destroy(mcmc_b200_ctx* ctx);
+
+/* P for this context's model. */
+int mcmc_b200_num_params(const mcmc_b200_ctx* ctx);
+
+/*
+ * Uploads one window's dataset.  Stands in for read_data + the H2D copies
+ * (io.h:42-86) — the file parsing itself is not part of this library.
+ * `global_window` keys the random streams, so a window gives the same chain
+ * wherever it is placed.  x/y may be host or device pointers (is_device).
+ * The library keeps its own repacked copy ([rows][24] floats: 22 features,
+ * a constant 1 and y); the caller's buffers are not referenced afterwards.
+ */
+int mcmc_b200_set_window_data(mcmc_b200_ctx* ctx, int window, int64_t global_window,
+                              const float* x, const float* y, int is_device);
+
+/*
+ * log p and its gradient at w, without touching the chain state: the
+ * reference's loss-only idiom mcmc_step<T,1> with eps = 0 on a zeroed Network
+ * (main.h:85-99) followed by get_loss_values (kernel_helpers.h:190-216).
+ *   w        [P] host
+ *   loglik   sum of per-row log-likelihoods      (loss_values[0..N))
+ *   logprior sum of per-parameter log-priors     (loss_values[N..N+P))
+ *   grad     [P] host, likelihood + prior gradient (grad_cur)
+ *   row_loss optional [rows] host
+ */
+int mcmc_b200_potential_and_grad(mcmc_b200_ctx* ctx, int window, const float* w, double* loglik,
+                                 double* logprior, float* grad, float* row_loss);
+
+/*
+ * L leapfrog steps on explicit host state: mcmc_step<T,L>
+ * (mcmc_step_ffma.h:395-427 / mcmc_step_tc.h:679-696).  First kick is a half
+ * kick with grad_prev, the closing half kick is NOT applied (it belongs to the
+ * accept ratio, kernel_helpers.h:163-175).  All vectors [P] host.
+ */
+int mcmc_b200_leapfrog(mcmc_b200_ctx* ctx, int window, int L, float eps, const float* w_prev,
+                       const float* mom_prev, const float* grad_prev, float* w_next,
+                       float* mom_next, float* grad_cur, double* loglik, double* logprior);
+
+/*
+ * Runs `n_iter` further HMC iterations on every window of the context:
+ * main_loop's sampling loop (main.h:204-287) with momentum draw, L leapfrog
+ * steps, accept ratio, accept/reject, step-size adaptation and sample store
+ * all on the device.  The first call also does the bootstrap evaluation at
+ * w = 0 (main.h:191-202).  Returns after the device work has finished.
+ */
+int mcmc_b200_run_chain(mcmc_b200_ctx* ctx, int n_iter);
+/* Same, but returns as soon as the work is queued on the context's stream. */
+int mcmc_b200_run_chain_async(mcmc_b200_ctx* ctx, int n_iter);
+int mcmc_b200_synchronize(mcmc_b200_ctx* ctx);
+/* The CUDA stream (cudaStream_t) all of this context's work is queued on. */
+void* mcmc_b200_stream(mcmc_b200_ctx* ctx);
+/* Restarts every chain at w = 0, iteration 0 (the data stays). */
+int mcmc_b200_reset_chain(mcmc_b200_ctx* ctx);
+
+/* Iterations done so far, accepted proposals and the current step size. */
+int mcmc_b200_chain_info(mcmc_b200_ctx* ctx, int window, int32_t* iterations, int32_t* accepted,
+                         float* eps);
+/* Current chain state [P] (prev_step_w, main.h:180) and its log-density parts. */
+int mcmc_b200_get_state(mcmc_b200_ctx* ctx, int window, float* w, float* grad, double* loglik,
+                        double* logprior);
+/* Stored samples (final_samples, main.h:183,277-283): `count` vectors of P
+ * floats starting at stored sample `first`, into host memory. */
+int mcmc_b200_get_samples(mcmc_b200_ctx* ctx, int window, int first, int count, float* out);
+/*
+ * Trace of the first cfg.trace_iters iterations: what a parity test needs to
+ * replay the chain on the CPU with the same draws.
+ *   momenta  optional [count][P]: the N(0,1) momentum drawn for each iteration
+ *   log_u    optional [count]   : log of the accept uniform
+ *   log_acpt optional [count]   : accept log-ratio (kernel_helpers.h:163-175)
+ *   accepted optional [count]
+ *   eps      optional [count]   : step size used by the iteration
+ */
+int mcmc_b200_get_trace(mcmc_b200_ctx* ctx, int window, int first, int count, float* momenta,
+                        float* log_u, double* log_acpt, int32_t* accepted, float* eps);
+
+/*
+ * Posterior-mean prediction: mean over stored samples [first, first+count) of
+ * the network output for each of n rows of xs ([n][D] host).  The reference
+ * evaluates only losses over its stored samples (output_final_loss,
+ * main.h:78-115); this is the matching forward-only pass.
+ */
+int mcmc_b200_predict_mean(mcmc_b200_ctx* ctx, int window, const float* xs, int64_t n, int first,
+                           int count, float* out);
+/* Mean log-likelihood / log-prior over stored samples: output_final_loss
+ * (main.h:78-115). */
+int mcmc_b200_final_loss(mcmc_b200_ctx* ctx, int window, int first, int count, double* mean_loglik,
+                         double* mean_logprior);
+
+/*
+ * Row sharding of ONE window over several GPUs (one process per GPU): every
+ * rank holds rows/nranks rows, and each leapfrog step sums the P-vector of
+ * gradient partials (plus the log-likelihood) over ranks with one NCCL
+ * allreduce.  The reference has no multi-GPU code; this is the mode its README
+ * table implies.  Rank 0 makes the id, the caller broadcasts the 128 bytes.
+ */
+int mcmc_b200_nccl_unique_id(unsigned char id[128]);
+int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* ctx, const unsigned char id[128], int rank,
+                                  int nranks);
+
+/*
+ * Drop-in for mcmc::mcmc_step<float, L> on caller-owned DEVICE buffers
+ * (mcmc_step_ffma.h:395-402).  Same argument meaning: x [N][D], y [N],
+ * grad_prev = complete gradient at weights_prev; on return weights_next,
+ * mom_next, the gradient at weights_next in grad_cur, grad_next zeroed,
+ * loss_values[0..N) per-row log-likelihood and [N..N+P) per-parameter
+ * log-prior.  Unlike the reference the caller's buffer roles are NOT rotated:
+ * outputs always land in the buffers named here.  Queued on `stream`.
+ * The context must have been created with n_windows = 1 and rows = N.
+ */
+int mcmc_b200_mcmc_step(mcmc_b200_ctx* ctx, const float* x, const float* y, const float* weights_prev,
+                        float* weights_next, const float* mom_prev, float* mom_next,
+                        const float* grad_prev, float* grad_cur, float* grad_next,
+                        float* loss_values, int L, float eps, void* stream);
+/*
+ * Drop-in for mcmc::log_acpt_prec (kernel_helpers.h:153-188) on DEVICE
+ * buffers: sum(new_loss - prev_loss) over n_loss entries plus the kinetic
+ * difference with the closing half kick; returns the scalar on the host
+ * (synchronises `stream`, as the reference does).
+ */
+int mcmc_b200_log_acpt(mcmc_b200_ctx* ctx, const float* prev_loss, const float* new_loss,
+                       int64_t n_loss, const float* prev_mom, const float* new_mom,
+                       const float* grad_cur, float eps, void* stream, float* out);
+
+/*
+ * Synthetic window generator (host code, no GPU): X ~ N(0,1), teacher weights
+ * ~ N(0, 0.3^2), y = teacher(X) + N(0, 0.05^2), all from Philox streams keyed
+ * by (seed, window).  Stands in for the reference's missing data file
+ * (global_params.h:65).  teacher is optional [P].
+ */
+int mcmc_b200_synth_window(uint64_t seed, int64_t window, int64_t rows, int D, int H, float* x,
+                           float* y, float* teacher);
+/* Host evaluation of the library's random streams (for tests). */
+float mcmc_b200_philox_normal(uint64_t seed, uint32_t window, uint32_t iteration, uint32_t stream,
+                              uint32_t index);
+void mcmc_b200_philox_raw(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
+
+/* Counters for benchmarks: kernels of this library launched on the context
+ * since creation (or since the last reset of the counter). */
+int64_t mcmc_b200_launch_count(mcmc_b200_ctx* ctx, int reset);
+/* Average device time in ms of the dominant (gradient) kernel over the last
+ * run_chain call, from CUDA events on the launching stream; <0 if unknown. */
+int mcmc_b200_chain_geometry(mcmc_b200_ctx* ctx, int* slices, int* ctas_per_sm, int* tile_rows);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MCMC_B200_H_ */

@@ -1,0 +1,889 @@
+// C-ABI of the library (declared in include/mcmc_b200.h): context and buffer
+// management, launch sequencing of the gradient / accept kernels, CUDA-graph
+// replay of whole HMC iterations, the optional NCCL allreduce for row sharding.
+// Host-side counterpart of the reference's main_loop / Network / mcmc_step
+// (include/mcmc/main.h:48-76, :117-308; mcmc_step_ffma.h:395-427).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#include "../../include/mcmc_b200.h"
+#include "chain.cuh"
+#include "common.cuh"
+#include "philox.h"
+
+using namespace mcmc_b200;
+
+#define API extern "C" __attribute__((visibility("default")))
+
+static thread_local std::string g_last_error;
+
+static int fail(int code, const std::string& msg) {
+  g_last_error = msg;
+  return code;
+}
+
+#define CK(call)                                                                              \
+  do {                                                                                        \
+    cudaError_t e_ = (call);                                                                  \
+    if (e_ != cudaSuccess)                                                                    \
+      return fail(MCMC_B200_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));    \
+  } while (0)
+
+// ---- NCCL through dlopen: no link-time dependency, and the copy already
+// loaded into the process (for instance by torch) is the one that is used ----
+namespace {
+struct NcclUniqueId { char internal[128]; };
+typedef void* NcclComm;
+struct NcclApi {
+  void* handle = nullptr;
+  int (*GetUniqueId)(NcclUniqueId*) = nullptr;
+  int (*CommInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
+  int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*CommDestroy)(NcclComm) = nullptr;
+  const char* (*GetErrorString)(int) = nullptr;
+  bool ok = false;
+};
+NcclApi g_nccl;
+
+bool nccl_load(std::string* why) {
+  if (g_nccl.ok) return true;
+  const char* env = getenv("MCMC_B200_NCCL_LIB");
+  const char* names[] = {env, "libnccl.so.2", "libnccl.so"};
+  for (const char* n : names) {
+    if (!n) continue;
+    g_nccl.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+    if (g_nccl.handle) break;
+  }
+  if (!g_nccl.handle) {
+    *why = std::string("dlopen(libnccl.so.2) failed: ") + dlerror();
+    return false;
+  }
+  g_nccl.GetUniqueId = (int (*)(NcclUniqueId*))dlsym(g_nccl.handle, "ncclGetUniqueId");
+  g_nccl.CommInitRank = (int (*)(NcclComm*, int, NcclUniqueId, int))dlsym(g_nccl.handle, "ncclCommInitRank");
+  g_nccl.AllReduce = (int (*)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t))dlsym(
+      g_nccl.handle, "ncclAllReduce");
+  g_nccl.CommDestroy = (int (*)(NcclComm))dlsym(g_nccl.handle, "ncclCommDestroy");
+  g_nccl.GetErrorString = (const char* (*)(int))dlsym(g_nccl.handle, "ncclGetErrorString");
+  if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy) {
+    *why = "NCCL symbols missing";
+    return false;
+  }
+  g_nccl.ok = true;
+  return true;
+}
+constexpr int kNcclFloat64 = 8;
+constexpr int kNcclSum = 0;
+}  // namespace
+
+struct mcmc_b200_ctx {
+  mcmc_b200_config cfg;
+  int device = 0, W = 0, P = 0, Pp = 0;
+  long long rows = 0, rows_pad = 0;
+  int num_sms = 0, ctas_per_sm = 1;
+  int slices = 1;      // CTAs per window in chain launches
+  int slices_x = 1;    // CTAs for single-window explicit calls
+  int tile_rows = 64;
+  cudaStream_t stream = nullptr;
+  // dataset
+  float* xaug = nullptr;
+  std::vector<char> window_set;
+  CUtensorMap tmap;
+  bool tmap_ok = false;
+  // chain state
+  float *wbuf[2] = {}, *mbuf[2] = {}, *w_cur = nullptr, *g_cur = nullptr, *m0 = nullptr;
+  float* partial[2] = {};
+  double* llp[2] = {};
+  double *red = nullptr, *ll_cur = nullptr, *lp_cur = nullptr;
+  float* eps = nullptr;
+  int *iter = nullptr, *n_accept = nullptr;
+  long long* gwin = nullptr;
+  float* samples = nullptr;
+  float *tr_mom = nullptr, *tr_log_u = nullptr, *tr_eps = nullptr;
+  double* tr_log_acpt = nullptr;
+  int* tr_accept = nullptr;
+  int* status = nullptr;
+  std::vector<long long> h_gwin;
+  bool bootstrapped = false;
+  int iters_done = 0;
+  // explicit-state scratch (one window)
+  float *xw[2] = {}, *xm[2] = {}, *xg = nullptr, *xpartial[2] = {}, *g_out = nullptr, *row_loss = nullptr;
+  float* scalar_f = nullptr;
+  double *xllp[2] = {}, *xred = nullptr, *scalars = nullptr;
+  // bound dataset of the drop-in mcmc_step
+  const float *bound_x = nullptr, *bound_y = nullptr;
+  // graph of one HMC iteration
+  cudaGraphExec_t graph_exec = nullptr;
+  bool graph_tried = false;
+  // row sharding
+  NcclComm comm = nullptr;
+  int nranks = 1, rank = 0;
+  long long launches = 0;
+  float* dbg = nullptr;
+  float* stage = nullptr;  // upload staging for one window: [rows][D] then [rows]
+  std::vector<void*> allocs;
+};
+
+static int dalloc(mcmc_b200_ctx* c, void** p, size_t bytes, bool zero = true) {
+  if (bytes == 0) bytes = 16;
+  cudaError_t e = cudaMalloc(p, bytes);
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_NOMEM, std::string("cudaMalloc: ") + cudaGetErrorString(e));
+  c->allocs.push_back(*p);
+  if (zero) {
+    e = cudaMemset(*p, 0, bytes);
+    if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, std::string("cudaMemset: ") + cudaGetErrorString(e));
+  }
+  return MCMC_B200_OK;
+}
+#define DA(ptr, bytes)                                                   \
+  do {                                                                   \
+    int r_ = dalloc(c, (void**)&(ptr), (bytes));                         \
+    if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }         \
+  } while (0)
+
+API const char* mcmc_b200_last_error(void) { return g_last_error.c_str(); }
+API int mcmc_b200_has_tf32(void) { return tf32_supported(40); }
+
+API void mcmc_b200_config_reference(mcmc_b200_config* cfg) {
+  memset(cfg, 0, sizeof(*cfg));
+  cfg->D = 22; cfg->H = 40;
+  cfg->likelihood = MCMC_B200_LIK_STUDENT_T;
+  cfg->precision = MCMC_B200_PREC_FP32;
+  cfg->lik_scale = 100.0; cfg->lik_df = 2.2; cfg->prior_scale = 200.0;
+  cfg->leapfrog_steps = 1000; cfg->burn_in = 100; cfg->adapt_steps = 100; cfg->sample_capacity = 800;
+  cfg->eps0 = 0.01; cfg->target_rate = 0.2; cfg->decrement = 0.1; cfg->increment = 0.01;
+  cfg->seed = 0; cfg->trace_iters = 0; cfg->slices = 0;
+}
+API void mcmc_b200_config_baseline(mcmc_b200_config* cfg) {
+  mcmc_b200_config_reference(cfg);
+  cfg->likelihood = MCMC_B200_LIK_GAUSSIAN;
+  cfg->lik_scale = 1.0; cfg->lik_df = 0.0; cfg->prior_scale = 1.0;
+  cfg->leapfrog_steps = 10; cfg->burn_in = 0; cfg->adapt_steps = 0;
+  cfg->eps0 = 1e-3;
+}
+
+static LikParams make_lik(const mcmc_b200_config& cfg) {
+  LikParams l;
+  const double pi = 3.14159265358979323846;
+  l.kind = cfg.likelihood;
+  l.inv_scale = (float)(1.0 / cfg.lik_scale);
+  if (cfg.likelihood == MCMC_B200_LIK_STUDENT_T) {
+    l.df = (float)cfg.lik_df;
+    l.inv_df = (float)(1.0 / cfg.lik_df);
+    l.norm = (float)(log(fabs(cfg.lik_scale)) + 0.5 * log(cfg.lik_df) + 0.5 * log(pi) +
+                     lgamma(0.5 * cfg.lik_df) - lgamma(0.5 * (cfg.lik_df + 1.0)));
+    l.g_scale = (float)((cfg.lik_df + 1.0) / cfg.lik_scale);
+    l.l_scale = (float)(-0.5 * (cfg.lik_df + 1.0));
+  } else {
+    l.df = 0.f;
+    l.inv_df = 0.f;
+    l.norm = (float)(0.5 * log(2.0 * pi) + log(cfg.lik_scale));
+    l.g_scale = (float)(1.0 / cfg.lik_scale);
+    l.l_scale = -0.5f;
+  }
+  return l;
+}
+static PriorParams make_prior(const mcmc_b200_config& cfg) {
+  PriorParams p;
+  const double pi = 3.14159265358979323846;
+  p.neg_inv_s2 = (float)(-1.0 / (cfg.prior_scale * cfg.prior_scale));
+  p.inv_s = (float)(1.0 / cfg.prior_scale);
+  p.norm = (float)(0.5 * log(2.0 * pi) + log(cfg.prior_scale));
+  return p;
+}
+
+static int make_tensor_map(mcmc_b200_ctx* c) {
+  typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                               const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                               CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                               CUtensorMapFloatOOBfill);
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  CK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (!fn || qres != cudaDriverEntryPointSuccess)
+    return fail(MCMC_B200_ERR_CUDA, "cuTensorMapEncodeTiled not available");
+  // [W * rows_pad][24] floats; the box is 32 floats wide so that a staged row
+  // is a full 128-byte swizzle span: columns 24..31 are out of bounds and
+  // arrive as zeros without being read.
+  cuuint64_t gdim[2] = {(cuuint64_t)KP, (cuuint64_t)((long long)c->W * c->rows_pad)};
+  cuuint64_t gstride[1] = {(cuuint64_t)(KP * sizeof(float))};
+  cuuint32_t box[2] = {32, (cuuint32_t)TF32_TILE};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = ((EncodeFn)fn)(&c->tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char b[96];
+    snprintf(b, sizeof b, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return fail(MCMC_B200_ERR_CUDA, b);
+  }
+  c->tmap_ok = true;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows, int64_t rows,
+                         mcmc_b200_ctx** out) {
+  if (!cfg || !out || n_windows < 1 || rows < 1) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (cfg->D != 22) return fail(MCMC_B200_ERR_UNSUPPORTED, "only D = 22 is built");
+  if (cfg->H != 40 && cfg->H != 128) return fail(MCMC_B200_ERR_UNSUPPORTED, "only H = 40 or 128 is built");
+  if (cfg->precision == MCMC_B200_PREC_TF32 && !tf32_supported(cfg->H))
+    return fail(MCMC_B200_ERR_UNSUPPORTED, "TF32 path is built for H = 40 only");
+  if (cfg->leapfrog_steps < 1 || cfg->lik_scale <= 0 || cfg->prior_scale <= 0)
+    return fail(MCMC_B200_ERR_INVALID, "bad sampler/model constants");
+  if (n_windows > 65535) return fail(MCMC_B200_ERR_INVALID, "at most 65535 windows per context");
+  int ndev = 0;
+  cudaError_t e0 = cudaGetDeviceCount(&ndev);
+  if (e0 != cudaSuccess || ndev == 0)
+    return fail(MCMC_B200_ERR_CUDA, "no CUDA device: this library has no CPU path");
+  if (device < 0 || device >= ndev) return fail(MCMC_B200_ERR_INVALID, "device ordinal out of range");
+  CK(cudaSetDevice(device));
+  cudaDeviceProp prop;
+  CK(cudaGetDeviceProperties(&prop, device));
+  if (prop.major != 10)
+    return fail(MCMC_B200_ERR_UNSUPPORTED, "kernels are built for sm_100a (B200) only");
+
+  mcmc_b200_ctx* c = new mcmc_b200_ctx();
+  c->cfg = *cfg;
+  c->device = device;
+  c->W = n_windows;
+  c->rows = rows;
+  c->rows_pad = (rows + TF32_TILE - 1) / TF32_TILE * TF32_TILE;
+  c->P = cfg->D * cfg->H + 2 * cfg->H + 1;
+  c->Pp = (c->P + 3) / 4 * 4;
+  c->num_sms = prop.multiProcessorCount;
+  const bool tf32 = cfg->precision == MCMC_B200_PREC_TF32;
+  c->tile_rows = tf32 ? TF32_TILE : fp32_tile_rows(cfg->H);
+  c->ctas_per_sm = tf32 ? tf32_max_ctas_per_sm(cfg->H) : fp32_max_ctas_per_sm(cfg->H);
+  if (c->ctas_per_sm < 1) c->ctas_per_sm = 1;
+  const long long n_tiles = c->rows_pad / c->tile_rows;
+  const long long capacity = (long long)c->num_sms * c->ctas_per_sm;
+  long long s = cfg->slices > 0 ? cfg->slices : capacity / n_windows;
+  if (s < 1) s = 1;
+  if (s > n_tiles) s = n_tiles;
+  if (s > MAX_SLICES) s = MAX_SLICES;
+  c->slices = (int)s;
+  long long sx = cfg->slices > 0 ? cfg->slices : capacity;
+  if (sx > n_tiles) sx = n_tiles;
+  if (sx > MAX_SLICES) sx = MAX_SLICES;
+  if (sx < 1) sx = 1;
+  c->slices_x = (int)sx;
+  c->window_set.assign(n_windows, 0);
+  c->h_gwin.assign(n_windows, 0);
+  cudaError_t es = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
+  if (es != cudaSuccess) { delete c; return fail(MCMC_B200_ERR_CUDA, "cudaStreamCreate failed"); }
+
+  const size_t W = n_windows, Pp = c->Pp, P = c->P;
+  DA(c->xaug, W * c->rows_pad * KP * sizeof(float));
+  for (int i = 0; i < 2; ++i) {
+    DA(c->wbuf[i], W * Pp * 4);
+    DA(c->mbuf[i], W * Pp * 4);
+    DA(c->partial[i], W * c->slices * Pp * 4);
+    DA(c->llp[i], W * c->slices * 8);
+    DA(c->xw[i], Pp * 4);
+    DA(c->xm[i], Pp * 4);
+    DA(c->xpartial[i], (size_t)c->slices_x * Pp * 4);
+    DA(c->xllp[i], (size_t)c->slices_x * 8);
+  }
+  DA(c->w_cur, W * Pp * 4);
+  DA(c->g_cur, W * Pp * 4);
+  DA(c->m0, W * Pp * 4);
+  DA(c->red, W * (Pp + 4) * 8);
+  DA(c->xred, (Pp + 4) * 8);
+  DA(c->ll_cur, W * 8);
+  DA(c->lp_cur, W * 8);
+  DA(c->eps, W * 4);
+  DA(c->iter, W * 4);
+  DA(c->n_accept, W * 4);
+  DA(c->gwin, W * 8);
+  DA(c->status, 4);
+  DA(c->xg, Pp * 4);
+  DA(c->g_out, Pp * 4);
+  DA(c->row_loss, (size_t)c->rows_pad * 4);
+  DA(c->scalars, 4 * 8);
+  DA(c->scalar_f, 16);
+  DA(c->dbg, 16384 * 4);
+  if (cfg->sample_capacity > 0) {
+    int r_ = dalloc(c, (void**)&c->samples, W * (size_t)cfg->sample_capacity * P * 4, false);
+    if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
+  }
+  if (cfg->trace_iters > 0) {
+    const size_t K = cfg->trace_iters;
+    DA(c->tr_mom, W * K * P * 4);
+    DA(c->tr_log_u, W * K * 4);
+    DA(c->tr_log_acpt, W * K * 8);
+    DA(c->tr_accept, W * K * 4);
+    DA(c->tr_eps, W * K * 4);
+  }
+  if (tf32) {
+    int r_ = make_tensor_map(c);
+    if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
+  }
+  std::vector<float> e(W, (float)cfg->eps0);
+  cudaMemcpy(c->eps, e.data(), W * 4, cudaMemcpyHostToDevice);
+  *out = c;
+  return MCMC_B200_OK;
+}
+
+API void mcmc_b200_destroy(mcmc_b200_ctx* c) {
+  if (!c) return;
+  cudaSetDevice(c->device);
+  if (c->stream) cudaStreamSynchronize(c->stream);
+  if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
+  if (c->comm && g_nccl.ok) g_nccl.CommDestroy(c->comm);
+  for (void* p : c->allocs) cudaFree(p);
+  if (c->stream) cudaStreamDestroy(c->stream);
+  delete c;
+}
+
+API int mcmc_b200_num_params(const mcmc_b200_ctx* c) { return c ? c->P : -1; }
+API void* mcmc_b200_stream(mcmc_b200_ctx* c) { return c ? (void*)c->stream : nullptr; }
+
+static int check_status(mcmc_b200_ctx* c) {
+  int st = 0;
+  CK(cudaMemcpyAsync(&st, c->status, 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  if (st != 0) {
+    cudaMemsetAsync(c->status, 0, 4, c->stream);
+    char b[96];
+    snprintf(b, sizeof b, "device-side wait ran out (code %d)", st);
+    return fail(MCMC_B200_ERR_TIMEOUT, b);
+  }
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_synchronize(mcmc_b200_ctx* c) {
+  if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
+  CK(cudaSetDevice(c->device));
+  return check_status(c);
+}
+
+API int mcmc_b200_set_window_data(mcmc_b200_ctx* c, int window, int64_t global_window, const float* x,
+                                  const float* y, int is_device) {
+  if (!c || !x || !y || window < 0 || window >= c->W) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  const size_t nx = (size_t)c->rows * c->cfg.D, ny = (size_t)c->rows;
+  const float *dx = x, *dy = y;
+  if (!is_device) {
+    if (!c->stage) {
+      int r = dalloc(c, (void**)&c->stage, (nx + ny) * 4, false);
+      if (r) return r;
+    }
+    CK(cudaMemcpyAsync(c->stage, x, nx * 4, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(c->stage + nx, y, ny * 4, cudaMemcpyHostToDevice, c->stream));
+    dx = c->stage;
+    dy = c->stage + nx;
+  }
+  cudaError_t e = launch_repack(dx, dy, c->xaug + (size_t)window * c->rows_pad * KP, c->rows, c->rows_pad,
+                                c->cfg.D, c->stream);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  c->h_gwin[window] = global_window;
+  c->window_set[window] = 1;
+  CK(cudaMemcpyAsync(c->gwin + window, &c->h_gwin[window], 8, cudaMemcpyHostToDevice, c->stream));
+  CK(cudaStreamSynchronize(c->stream));  // the caller's buffers are free again on return
+  if (window == 0) { c->bound_x = nullptr; c->bound_y = nullptr; }
+  return MCMC_B200_OK;
+}
+
+// ---- launch helpers ------------------------------------------------------
+static GradParams base_grad_params(mcmc_b200_ctx* c) {
+  GradParams g;
+  memset(&g, 0, sizeof g);
+  g.xaug = c->xaug;
+  g.window_stride = c->rows_pad * KP;
+  g.n_rows = (int)c->rows;
+  g.n_tiles = (int)(c->rows_pad / c->tile_rows);
+  g.P = c->P;
+  g.Pp = c->Pp;
+  g.lik = make_lik(c->cfg);
+  g.prior = make_prior(c->cfg);
+  g.status = c->status;
+  return g;
+}
+
+static int launch_grad(mcmc_b200_ctx* c, const GradParams& g, int slices, int windows, cudaStream_t st,
+                       float* dbg = nullptr) {
+  cudaError_t e;
+  if (c->cfg.precision == MCMC_B200_PREC_TF32)
+    e = launch_grad_tf32(c->cfg.H, &c->tmap, g, slices, windows, dbg, st);
+  else
+    e = launch_grad_fp32(c->cfg.H, g, slices, windows, st);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, std::string("gradient kernel launch: ") + cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
+static int allreduce(mcmc_b200_ctx* c, double* buf, size_t count, cudaStream_t st) {
+  int r = g_nccl.AllReduce(buf, buf, count, kNcclFloat64, kNcclSum, c->comm, st);
+  if (r != 0)
+    return fail(MCMC_B200_ERR_NCCL, std::string("ncclAllReduce: ") +
+                                        (g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "error"));
+  return MCMC_B200_OK;
+}
+
+static AcceptParams base_accept_params(mcmc_b200_ctx* c) {
+  AcceptParams a;
+  memset(&a, 0, sizeof a);
+  a.P = c->P;
+  a.Pp = c->Pp;
+  a.prior = make_prior(c->cfg);
+  a.seed = c->cfg.seed;
+  return a;
+}
+
+static void fill_chain_accept(mcmc_b200_ctx* c, AcceptParams& a, int mode, int L) {
+  a.mode = mode;
+  a.slices = c->slices;
+  const int last = (mode == ACC_BOOTSTRAP) ? 0 : (L - 1) & 1;
+  a.partial = c->partial[last];
+  a.ll_partial = c->llp[last];
+  a.red_in = c->comm ? c->red : nullptr;
+  a.w_new = (mode == ACC_BOOTSTRAP) ? c->wbuf[0] : c->wbuf[L & 1];
+  a.m_new = (mode == ACC_BOOTSTRAP) ? c->mbuf[0] : c->mbuf[L & 1];
+  a.m0 = c->m0;
+  a.w_cur = c->w_cur;
+  a.g_cur = c->g_cur;
+  a.ll_cur = c->ll_cur;
+  a.lp_cur = c->lp_cur;
+  a.eps = c->eps;
+  a.iter = c->iter;
+  a.n_accept = c->n_accept;
+  a.gwin = c->gwin;
+  a.w_start = c->wbuf[0];
+  a.m_start = c->mbuf[0];
+  a.samples = c->samples;
+  a.sample_capacity = c->samples ? c->cfg.sample_capacity : 0;
+  a.burn_in = c->cfg.burn_in;
+  a.adapt_steps = c->cfg.adapt_steps;
+  a.log_target = (float)log(c->cfg.target_rate);
+  a.dec_adj = -(float)c->cfg.decrement / (1.f + (float)c->cfg.decrement);
+  a.inc_adj = (float)c->cfg.increment;
+  a.trace_iters = c->cfg.trace_iters;
+  a.tr_mom = c->tr_mom;
+  a.tr_log_u = c->tr_log_u;
+  a.tr_log_acpt = c->tr_log_acpt;
+  a.tr_accept = c->tr_accept;
+  a.tr_eps = c->tr_eps;
+}
+
+// queue one gradient evaluation for all windows (+ the allreduce when sharded)
+static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
+  GradParams g = base_grad_params(c);
+  g.mode = mode;
+  g.w_in = c->wbuf[s & 1];
+  g.m_in = c->mbuf[s & 1];
+  g.w_out = c->wbuf[(s + 1) & 1];
+  g.m_out = c->mbuf[(s + 1) & 1];
+  g.g_carried = c->g_cur;
+  g.partial_in = c->partial[(s + 1) & 1];
+  g.slices_in = c->slices;
+  g.red_in = (c->comm && mode == MODE_NEXT) ? c->red : nullptr;
+  g.partial_out = c->partial[s & 1];
+  g.ll_out = c->llp[s & 1];
+  g.eps = c->eps;
+  int r = launch_grad(c, g, c->slices, c->W, st);
+  if (r) return r;
+  if (c->comm) {
+    cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->P, c->Pp, c->red,
+                                           c->W, st);
+    c->launches++;
+    if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+    r = allreduce(c, c->red, (size_t)c->W * (c->Pp + 4), st);
+    if (r) return r;
+  }
+  return MCMC_B200_OK;
+}
+
+static int queue_iteration(mcmc_b200_ctx* c, cudaStream_t st) {
+  const int L = c->cfg.leapfrog_steps;
+  for (int s = 0; s < L; ++s) {
+    int r = chain_grad(c, s == 0 ? MODE_FIRST : MODE_NEXT, s, st);
+    if (r) return r;
+  }
+  AcceptParams a = base_accept_params(c);
+  fill_chain_accept(c, a, ACC_ITERATE, L);
+  cudaError_t e = launch_accept(a, c->W, st);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
+static int bootstrap(mcmc_b200_ctx* c) {
+  for (int w = 0; w < c->W; ++w)
+    if (!c->window_set[w]) return fail(MCMC_B200_ERR_INVALID, "a window has no data yet");
+  // main.h:52,182-185: the chain starts at w = 0
+  const size_t n = (size_t)c->W * c->Pp * 4;
+  CK(cudaMemsetAsync(c->wbuf[0], 0, n, c->stream));
+  CK(cudaMemsetAsync(c->mbuf[0], 0, n, c->stream));
+  CK(cudaMemsetAsync(c->iter, 0, (size_t)c->W * 4, c->stream));
+  CK(cudaMemsetAsync(c->n_accept, 0, (size_t)c->W * 4, c->stream));
+  std::vector<float> e(c->W, (float)c->cfg.eps0);
+  CK(cudaMemcpyAsync(c->eps, e.data(), (size_t)c->W * 4, cudaMemcpyHostToDevice, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  int r = chain_grad(c, MODE_EVAL, 0, c->stream);
+  if (r) return r;
+  AcceptParams a = base_accept_params(c);
+  fill_chain_accept(c, a, ACC_BOOTSTRAP, 1);
+  cudaError_t er = launch_accept(a, c->W, c->stream);
+  c->launches++;
+  if (er != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(er));
+  c->bootstrapped = true;
+  c->iters_done = 0;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_reset_chain(mcmc_b200_ctx* c) {
+  if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  c->bootstrapped = false;
+  c->iters_done = 0;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_run_chain_async(mcmc_b200_ctx* c, int n_iter) {
+  if (!c || n_iter < 0) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  if (!c->bootstrapped) {
+    int r = bootstrap(c);
+    if (r) return r;
+  }
+  if (n_iter == 0) return MCMC_B200_OK;
+  // One HMC iteration (L gradient launches + the accept kernel) is captured
+  // once and replayed: launch cost stays off the critical path.
+  if (!c->graph_tried) {
+    c->graph_tried = true;
+    const long long launches_before = c->launches;
+    cudaGraph_t graph = nullptr;
+    cudaError_t e = cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+      int r = queue_iteration(c, c->stream);
+      e = cudaStreamEndCapture(c->stream, &graph);
+      if (r == MCMC_B200_OK && e == cudaSuccess && graph) {
+        e = cudaGraphInstantiate(&c->graph_exec, graph, 0);
+        if (e != cudaSuccess) c->graph_exec = nullptr;
+      }
+      if (graph) cudaGraphDestroy(graph);
+    }
+    cudaGetLastError();
+    c->launches = launches_before;
+  }
+  const long long per_iter = (long long)c->cfg.leapfrog_steps * (c->comm ? 2 : 1) + 1;
+  for (int i = 0; i < n_iter; ++i) {
+    if (c->graph_exec) {
+      CK(cudaGraphLaunch(c->graph_exec, c->stream));
+      c->launches += per_iter;
+    } else {
+      int r = queue_iteration(c, c->stream);
+      if (r) return r;
+    }
+  }
+  c->iters_done += n_iter;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_run_chain(mcmc_b200_ctx* c, int n_iter) {
+  int r = mcmc_b200_run_chain_async(c, n_iter);
+  if (r) return r;
+  return check_status(c);
+}
+
+API int mcmc_b200_chain_info(mcmc_b200_ctx* c, int window, int32_t* iterations, int32_t* accepted,
+                             float* eps) {
+  if (!c || window < 0 || window >= c->W) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  if (iterations) CK(cudaMemcpy(iterations, c->iter + window, 4, cudaMemcpyDeviceToHost));
+  if (accepted) CK(cudaMemcpy(accepted, c->n_accept + window, 4, cudaMemcpyDeviceToHost));
+  if (eps) CK(cudaMemcpy(eps, c->eps + window, 4, cudaMemcpyDeviceToHost));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_get_state(mcmc_b200_ctx* c, int window, float* w, float* grad, double* loglik,
+                            double* logprior) {
+  if (!c || window < 0 || window >= c->W) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  const size_t o = (size_t)window * c->Pp;
+  if (w) CK(cudaMemcpy(w, c->w_cur + o, (size_t)c->P * 4, cudaMemcpyDeviceToHost));
+  if (grad) CK(cudaMemcpy(grad, c->g_cur + o, (size_t)c->P * 4, cudaMemcpyDeviceToHost));
+  if (loglik) CK(cudaMemcpy(loglik, c->ll_cur + window, 8, cudaMemcpyDeviceToHost));
+  if (logprior) CK(cudaMemcpy(logprior, c->lp_cur + window, 8, cudaMemcpyDeviceToHost));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_get_samples(mcmc_b200_ctx* c, int window, int first, int count, float* out) {
+  if (!c || !out || window < 0 || window >= c->W || first < 0 || count < 0 || !c->samples ||
+      first + count > c->cfg.sample_capacity)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments or no sample storage");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  const size_t P = c->P;
+  CK(cudaMemcpy(out, c->samples + ((size_t)window * c->cfg.sample_capacity + first) * P,
+                (size_t)count * P * 4, cudaMemcpyDeviceToHost));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_get_trace(mcmc_b200_ctx* c, int window, int first, int count, float* momenta,
+                            float* log_u, double* log_acpt, int32_t* accepted, float* eps) {
+  if (!c || window < 0 || window >= c->W || first < 0 || count < 0 ||
+      first + count > c->cfg.trace_iters)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments or trace not enabled");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  const size_t K = c->cfg.trace_iters, P = c->P, o = (size_t)window * K + first;
+  if (momenta) CK(cudaMemcpy(momenta, c->tr_mom + o * P, (size_t)count * P * 4, cudaMemcpyDeviceToHost));
+  if (log_u) CK(cudaMemcpy(log_u, c->tr_log_u + o, (size_t)count * 4, cudaMemcpyDeviceToHost));
+  if (log_acpt) CK(cudaMemcpy(log_acpt, c->tr_log_acpt + o, (size_t)count * 8, cudaMemcpyDeviceToHost));
+  if (accepted) CK(cudaMemcpy(accepted, c->tr_accept + o, (size_t)count * 4, cudaMemcpyDeviceToHost));
+  if (eps) CK(cudaMemcpy(eps, c->tr_eps + o, (size_t)count * 4, cudaMemcpyDeviceToHost));
+  return MCMC_B200_OK;
+}
+
+// ---- explicit-state calls (one window) -------------------------------------
+// L leapfrog steps from (w0, m0, g0) on device; results in xw/xm[L&1], g_out, scalars.
+static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, const float* w0,
+                          const float* m0, const float* g0, float* w_last, float* m_last,
+                          float* g_out, float* row_loss, float* prior_loss, cudaStream_t st,
+                          bool eval_only) {
+  const int S = c->slices_x;
+  for (int s = 0; s < L; ++s) {
+    GradParams g = base_grad_params(c);
+    g.data_window0 = data_window;
+    g.mode = eval_only ? MODE_EVAL : (s == 0 ? MODE_FIRST : MODE_NEXT);
+    g.w_in = s == 0 ? w0 : c->xw[s & 1];
+    g.m_in = s == 0 ? m0 : c->xm[s & 1];
+    const bool last = s == L - 1;
+    g.w_out = (last && w_last) ? w_last : c->xw[(s + 1) & 1];
+    g.m_out = (last && m_last) ? m_last : c->xm[(s + 1) & 1];
+    g.g_carried = g0;
+    g.partial_in = c->xpartial[(s + 1) & 1];
+    g.slices_in = S;
+    g.red_in = (c->comm && g.mode == MODE_NEXT) ? c->xred : nullptr;
+    g.partial_out = c->xpartial[s & 1];
+    g.ll_out = c->xllp[s & 1];
+    g.eps = nullptr;
+    g.eps_scalar = eps;
+    g.row_loss = last ? row_loss : nullptr;
+    g.row_loss_stride = 0;
+    int r = launch_grad(c, g, S, 1, st, (eval_only && c->cfg.precision == MCMC_B200_PREC_TF32) ? c->dbg : nullptr);
+    if (r) return r;
+    if (c->comm) {
+      cudaError_t e = launch_reduce_partials(c->xpartial[s & 1], c->xllp[s & 1], S, c->P, c->Pp, c->xred, 1, st);
+      c->launches++;
+      if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+      r = allreduce(c, c->xred, (size_t)(c->Pp + 4), st);
+      if (r) return r;
+    }
+  }
+  AcceptParams a = base_accept_params(c);
+  a.mode = ACC_FINALIZE;
+  a.slices = S;
+  a.partial = c->xpartial[(L - 1) & 1];
+  a.ll_partial = c->xllp[(L - 1) & 1];
+  a.red_in = c->comm ? c->xred : nullptr;
+  a.w_new = eval_only ? w0 : ((w_last) ? w_last : c->xw[L & 1]);
+  a.g_out = g_out;
+  a.prior_loss_out = prior_loss;
+  a.scalars_out = c->scalars;
+  cudaError_t e = launch_accept(a, 1, st);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_potential_and_grad(mcmc_b200_ctx* c, int window, const float* w, double* loglik,
+                                     double* logprior, float* grad, float* row_loss) {
+  if (!c || !w || window < 0 || window >= c->W) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (!c->window_set[window]) return fail(MCMC_B200_ERR_INVALID, "window has no data yet");
+  CK(cudaSetDevice(c->device));
+  CK(cudaMemcpyAsync(c->xw[0], w, (size_t)c->P * 4, cudaMemcpyHostToDevice, c->stream));
+  int r = explicit_steps(c, window, 1, 0.f, c->xw[0], c->xm[0], c->xg, nullptr, nullptr, c->g_out,
+                         row_loss ? c->row_loss : nullptr, nullptr, c->stream, true);
+  if (r) return r;
+  double sc[2];
+  CK(cudaMemcpyAsync(sc, c->scalars, 16, cudaMemcpyDeviceToHost, c->stream));
+  if (grad) CK(cudaMemcpyAsync(grad, c->g_out, (size_t)c->P * 4, cudaMemcpyDeviceToHost, c->stream));
+  if (row_loss)
+    CK(cudaMemcpyAsync(row_loss, c->row_loss, (size_t)c->rows * 4, cudaMemcpyDeviceToHost, c->stream));
+  r = check_status(c);
+  if (r) return r;
+  if (loglik) *loglik = sc[0];
+  if (logprior) *logprior = sc[1];
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_leapfrog(mcmc_b200_ctx* c, int window, int L, float eps, const float* w_prev,
+                           const float* mom_prev, const float* grad_prev, float* w_next,
+                           float* mom_next, float* grad_cur, double* loglik, double* logprior) {
+  if (!c || !w_prev || !mom_prev || !grad_prev || L < 1 || window < 0 || window >= c->W)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (!c->window_set[window]) return fail(MCMC_B200_ERR_INVALID, "window has no data yet");
+  CK(cudaSetDevice(c->device));
+  const size_t n = (size_t)c->P * 4;
+  CK(cudaMemcpyAsync(c->xw[0], w_prev, n, cudaMemcpyHostToDevice, c->stream));
+  CK(cudaMemcpyAsync(c->xm[0], mom_prev, n, cudaMemcpyHostToDevice, c->stream));
+  CK(cudaMemcpyAsync(c->xg, grad_prev, n, cudaMemcpyHostToDevice, c->stream));
+  int r = explicit_steps(c, window, L, eps, c->xw[0], c->xm[0], c->xg, nullptr, nullptr, c->g_out, nullptr,
+                         nullptr, c->stream, false);
+  if (r) return r;
+  double sc[2];
+  CK(cudaMemcpyAsync(sc, c->scalars, 16, cudaMemcpyDeviceToHost, c->stream));
+  if (w_next) CK(cudaMemcpyAsync(w_next, c->xw[L & 1], n, cudaMemcpyDeviceToHost, c->stream));
+  if (mom_next) CK(cudaMemcpyAsync(mom_next, c->xm[L & 1], n, cudaMemcpyDeviceToHost, c->stream));
+  if (grad_cur) CK(cudaMemcpyAsync(grad_cur, c->g_out, n, cudaMemcpyDeviceToHost, c->stream));
+  r = check_status(c);
+  if (r) return r;
+  if (loglik) *loglik = sc[0];
+  if (logprior) *logprior = sc[1];
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_mcmc_step(mcmc_b200_ctx* c, const float* x, const float* y, const float* weights_prev,
+                            float* weights_next, const float* mom_prev, float* mom_next,
+                            const float* grad_prev, float* grad_cur, float* grad_next,
+                            float* loss_values, int L, float eps, void* stream) {
+  if (!c || !x || !y || !weights_prev || !weights_next || !mom_prev || !mom_next || !grad_prev ||
+      !grad_cur || L < 1)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (c->W != 1) return fail(MCMC_B200_ERR_INVALID, "mcmc_step needs a context with one window");
+  CK(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  if (x != c->bound_x || y != c->bound_y) {
+    // first use of this dataset: repack it (io.h:82-85 is where the reference uploads it)
+    cudaError_t e = launch_repack(x, y, c->xaug, c->rows, c->rows_pad, c->cfg.D, st);
+    c->launches++;
+    if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+    c->bound_x = x;
+    c->bound_y = y;
+    c->window_set[0] = 1;
+  }
+  int r = explicit_steps(c, 0, L, eps, weights_prev, mom_prev, grad_prev, weights_next, mom_next, grad_cur,
+                         loss_values, loss_values ? loss_values + c->rows : nullptr, st, false);
+  if (r) return r;
+  if (grad_next) CK(cudaMemsetAsync(grad_next, 0, (size_t)c->P * 4, st));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_log_acpt(mcmc_b200_ctx* c, const float* prev_loss, const float* new_loss,
+                           int64_t n_loss, const float* prev_mom, const float* new_mom,
+                           const float* grad_cur, float eps, void* stream, float* out) {
+  if (!c || !prev_loss || !new_loss || !prev_mom || !new_mom || !grad_cur || !out)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  cudaStream_t st = (cudaStream_t)stream;
+  cudaError_t e = launch_log_acpt(prev_loss, new_loss, n_loss, prev_mom, new_mom, grad_cur, c->P, eps,
+                                  c->scalar_f, st);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  CK(cudaMemcpyAsync(out, c->scalar_f, 4, cudaMemcpyDeviceToHost, st));
+  CK(cudaStreamSynchronize(st));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_predict_mean(mcmc_b200_ctx* c, int window, const float* xs, int64_t n, int first,
+                               int count, float* out) {
+  if (!c || !xs || !out || n < 1 || window < 0 || window >= c->W || first < 0 || count < 1 ||
+      !c->samples || first + count > c->cfg.sample_capacity)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments or no sample storage");
+  CK(cudaSetDevice(c->device));
+  float *dx = nullptr, *dout = nullptr;
+  CK(cudaMalloc(&dx, (size_t)n * c->cfg.D * 4));
+  cudaError_t e = cudaMalloc(&dout, (size_t)n * 4);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(dx, xs, (size_t)n * c->cfg.D * 4, cudaMemcpyHostToDevice, c->stream);
+  if (e == cudaSuccess) {
+    e = launch_predict(c->cfg.H, dx, n, c->samples + ((size_t)window * c->cfg.sample_capacity + first) * c->P,
+                       count, c->P, dout, c->stream);
+    c->launches++;
+  }
+  if (e == cudaSuccess) e = cudaMemcpyAsync(out, dout, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+  cudaFree(dx);
+  if (dout) cudaFree(dout);
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_final_loss(mcmc_b200_ctx* c, int window, int first, int count, double* mean_loglik,
+                             double* mean_logprior) {
+  if (!c || window < 0 || window >= c->W || first < 0 || count < 1 || !c->samples ||
+      first + count > c->cfg.sample_capacity)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments or no sample storage");
+  CK(cudaSetDevice(c->device));
+  std::vector<double> sc((size_t)count * 2);
+  double a = 0, b = 0;
+  for (int s = 0; s < count; ++s) {
+    const float* w = c->samples + ((size_t)window * c->cfg.sample_capacity + first + s) * c->P;
+    int r = explicit_steps(c, window, 1, 0.f, w, c->xm[0], c->xg, nullptr, nullptr, c->g_out, nullptr, nullptr,
+                           c->stream, true);
+    if (r) return r;
+    CK(cudaMemcpyAsync(&sc[2 * s], c->scalars, 16, cudaMemcpyDeviceToHost, c->stream));
+  }
+  int r = check_status(c);
+  if (r) return r;
+  for (int s = 0; s < count; ++s) { a += sc[2 * s]; b += sc[2 * s + 1]; }
+  if (mean_loglik) *mean_loglik = a / count;
+  if (mean_logprior) *mean_logprior = b / count;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_nccl_unique_id(unsigned char id[128]) {
+  std::string why;
+  if (!nccl_load(&why)) return fail(MCMC_B200_ERR_NCCL, why);
+  NcclUniqueId u;
+  int r = g_nccl.GetUniqueId(&u);
+  if (r != 0) return fail(MCMC_B200_ERR_NCCL, "ncclGetUniqueId failed");
+  memcpy(id, u.internal, 128);
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* c, const unsigned char id[128], int rank, int nranks) {
+  if (!c || !id || nranks < 1 || rank < 0 || rank >= nranks) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (c->bootstrapped) return fail(MCMC_B200_ERR_INVALID, "enable row sharding before the chain starts");
+  std::string why;
+  if (!nccl_load(&why)) return fail(MCMC_B200_ERR_NCCL, why);
+  CK(cudaSetDevice(c->device));
+  NcclUniqueId u;
+  memcpy(u.internal, id, 128);
+  int r = g_nccl.CommInitRank(&c->comm, nranks, u, rank);
+  if (r != 0) {
+    c->comm = nullptr;
+    return fail(MCMC_B200_ERR_NCCL, std::string("ncclCommInitRank: ") +
+                                        (g_nccl.GetErrorString ? g_nccl.GetErrorString(r) : "error"));
+  }
+  c->rank = rank;
+  c->nranks = nranks;
+  return MCMC_B200_OK;
+}
+
+API int64_t mcmc_b200_launch_count(mcmc_b200_ctx* c, int reset) {
+  if (!c) return -1;
+  long long v = c->launches;
+  if (reset) c->launches = 0;
+  return v;
+}
+
+API int mcmc_b200_chain_geometry(mcmc_b200_ctx* c, int* slices, int* ctas_per_sm, int* tile_rows) {
+  if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
+  if (slices) *slices = c->slices;
+  if (ctas_per_sm) *ctas_per_sm = c->ctas_per_sm;
+  if (tile_rows) *tile_rows = c->tile_rows;
+  return MCMC_B200_OK;
+}
+
+// debugging aid for the tensor-core path: first-tile pre-activations and the raw
+// backward accumulator of CTA (0,0) of the last potential_and_grad call
+extern "C" __attribute__((visibility("default"))) int mcmc_b200_debug_dump(mcmc_b200_ctx* c, float* out,
+                                                                             int n_floats) {
+  if (!c || !out || n_floats > 16384) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  CK(cudaMemcpy(out, c->dbg, (size_t)n_floats * 4, cudaMemcpyDeviceToHost));
+  return MCMC_B200_OK;
+}

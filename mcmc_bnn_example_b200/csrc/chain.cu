@@ -1,0 +1,271 @@
+// Per-iteration kernels of the HMC driver, one CTA per window:
+//   * hmc_accept_kernel — the fixed-order sum of the gradient partials, the
+//     prior terms, the closing half kick, the Hamiltonian difference, the
+//     Philox accept draw, accept/reject, step-size adaptation, sample store and
+//     the momentum draw of the next iteration.  It replaces the reference's
+//     momentum-draw launch (main.h:207-216), log_acpt_prec (two launches, a
+//     D2H copy and a stream synchronise, kernel_helpers.h:153-188), the host
+//     accept draw (main.h:235-239), the six D2D copies (main.h:242-265), the
+//     host step-size update (main.h:266-276) and the sample copy (:277-283):
+//     no host round trip is left inside an iteration.
+//   * repack_kernel — [N][22] + [N] -> [N_pad][24] rows {x, 1, y}.
+//   * reduce_partials_kernel — row sharding: the vector that is all-reduced.
+//   * predict_kernel, log_acpt_kernel — forward-only pass over stored samples
+//     and the drop-in accept ratio on caller buffers.
+#include "common.cuh"
+#include "chain.cuh"
+#include "philox.h"
+
+namespace mcmc_b200 {
+
+constexpr int ACC_THREADS = 256;
+
+__global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptParams a) {
+  __shared__ double dsc[32];
+  __shared__ int s_accept;
+  __shared__ float s_eps;
+  const int win = blockIdx.x;
+  const int tid = threadIdx.x;
+  const size_t o = (size_t)win * a.Pp;
+  const int iter = (a.mode == ACC_ITERATE) ? a.iter[win] : 0;
+  const float eps = a.eps ? a.eps[win] : 0.f;
+  const uint32_t gwin = a.gwin ? (uint32_t)a.gwin[win] : 0u;
+
+  // log-likelihood of the proposal: fixed-order sum of the slice partials
+  double ll_new;
+  if (a.red_in) {
+    ll_new = a.red_in[(size_t)win * (a.Pp + 4) + a.Pp];
+  } else {
+    ll_new = 0.0;
+    for (int s = 0; s < a.slices; ++s) ll_new += a.ll_partial[(size_t)win * a.slices + s];
+  }
+
+  constexpr int MAXPT = 16;  // parameters per thread (P <= 4096)
+  float wv[MAXPT], gv[MAXPT];
+  double lp_loc = 0.0, dk_loc = 0.0;
+  int n = 0;
+  for (int p = tid; p < a.P; p += ACC_THREADS, ++n) {
+    const float w = a.w_new[o + p];
+    float g;
+    if (a.red_in) {
+      g = (float)a.red_in[(size_t)win * (a.Pp + 4) + p];
+    } else {
+      const float* pi = a.partial + (size_t)win * a.slices * a.Pp + p;
+      g = 0.f;
+      for (int s = 0; s < a.slices; ++s) g += pi[(size_t)s * a.Pp];
+    }
+    g = fmaf(w, a.prior.neg_inv_s2, g);
+    const float q = w * a.prior.inv_s;
+    const float pl = fmaf(-0.5f * q, q, -a.prior.norm);
+    lp_loc += (double)pl;
+    if (a.prior_loss_out) a.prior_loss_out[p] = pl;
+    if (a.mode == ACC_ITERATE) {
+      // closing half kick (kernel_helpers.h:169-172)
+      const float mf = fmaf(eps * 0.5f, g, a.m_new[o + p]);
+      const float m0 = a.m0[o + p];
+      dk_loc += 0.5 * ((double)m0 * (double)m0 - (double)mf * (double)mf);
+    }
+    wv[n] = w;
+    gv[n] = g;
+  }
+  const double lp_new = block_sum_f64(lp_loc, dsc);
+  const double dk = (a.mode == ACC_ITERATE) ? block_sum_f64(dk_loc, dsc) : 0.0;
+
+  if (a.mode == ACC_FINALIZE) {
+    n = 0;
+    for (int p = tid; p < a.P; p += ACC_THREADS, ++n) a.g_out[p] = gv[n];
+    if (tid == 0) {
+      a.scalars_out[0] = ll_new;
+      a.scalars_out[1] = lp_new;
+    }
+    return;
+  }
+
+  if (tid == 0) {
+    int acc = 1;
+    float eps_next = eps;
+    if (a.mode == ACC_ITERATE) {
+      const double la = (ll_new - a.ll_cur[win]) + (lp_new - a.lp_cur[win]) + dk;
+      const float la_f = (float)la;
+      const float log_u = logf(philox_accept_uniform(a.seed, gwin, (uint32_t)iter));
+      acc = log_u < la_f;  // main.h:242; a NaN ratio rejects
+      if (iter < a.adapt_steps) {  // main.h:266-276
+        const float lmr = fminf(la_f, 0.f);
+        const float adj = lmr < a.log_target ? a.dec_adj : a.inc_adj;
+        eps_next = eps + eps * adj;
+      }
+      if (iter < a.trace_iters) {
+        const size_t ti = (size_t)win * a.trace_iters + iter;
+        a.tr_log_u[ti] = log_u;
+        a.tr_log_acpt[ti] = la;
+        a.tr_accept[ti] = acc;
+        a.tr_eps[ti] = eps;
+      }
+      a.n_accept[win] += acc;
+      a.iter[win] = iter + 1;
+      a.eps[win] = eps_next;
+    }
+    if (acc) {
+      a.ll_cur[win] = ll_new;
+      a.lp_cur[win] = lp_new;
+    }
+    s_accept = acc;
+    s_eps = eps_next;
+  }
+  __syncthreads();
+  const int acc = s_accept;
+  const int next_iter = (a.mode == ACC_ITERATE) ? iter + 1 : 0;
+  const int store = (a.mode == ACC_ITERATE) ? iter - a.burn_in : -1;
+  n = 0;
+  for (int p = tid; p < a.P; p += ACC_THREADS, ++n) {
+    float w_state;
+    if (acc) {
+      w_state = wv[n];
+      a.w_cur[o + p] = wv[n];
+      a.g_cur[o + p] = gv[n];
+    } else {
+      w_state = a.w_cur[o + p];
+    }
+    if (store >= 0 && store < a.sample_capacity)
+      a.samples[((size_t)win * a.sample_capacity + store) * a.P + p] = w_state;
+    // start of the next iteration: position, fresh momentum (main.h:207-218)
+    const float m = philox_normal(a.seed, gwin, (uint32_t)next_iter, STREAM_MOMENTUM, (uint32_t)p);
+    a.w_start[o + p] = w_state;
+    a.m_start[o + p] = m;
+    a.m0[o + p] = m;
+    if (next_iter < a.trace_iters)
+      a.tr_mom[((size_t)win * a.trace_iters + next_iter) * a.P + p] = m;
+  }
+}
+
+cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st) {
+  hmc_accept_kernel<<<windows, ACC_THREADS, 0, st>>>(a);
+  return cudaGetLastError();
+}
+
+// ---- dataset repack ------------------------------------------------------
+__global__ void repack_kernel(const float* __restrict__ x, const float* __restrict__ y,
+                              float* __restrict__ out, long long n_rows, long long rows_pad, int D) {
+  const long long total = rows_pad * KP;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / KP;
+    const int c = (int)(i - r * KP);
+    float v = 0.f;
+    if (r < n_rows) {
+      if (c < D) v = x[r * D + c];
+      else if (c == COL_ONE) v = 1.f;
+      else if (c == COL_Y) v = y[r];
+    }
+    out[i] = v;
+  }
+}
+
+cudaError_t launch_repack(const float* x, const float* y, float* out, long long n_rows,
+                          long long rows_pad, int D, cudaStream_t st) {
+  const long long total = rows_pad * KP;
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  repack_kernel<<<blocks, 256, 0, st>>>(x, y, out, n_rows, rows_pad, D);
+  return cudaGetLastError();
+}
+
+// ---- row sharding: this rank's sums, as doubles, ready for the allreduce ---
+__global__ void reduce_partials_kernel(const float* __restrict__ partial,
+                                       const double* __restrict__ ll_partial, int slices, int P,
+                                       int Pp, double* __restrict__ red) {
+  const int win = blockIdx.y;
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  double* r = red + (size_t)win * (Pp + 4);
+  if (p < P) {
+    const float* pi = partial + (size_t)win * slices * Pp + p;
+    float g = 0.f;
+    for (int s = 0; s < slices; ++s) g += pi[(size_t)s * Pp];
+    r[p] = (double)g;
+  } else if (p == Pp) {
+    double s = 0.0;
+    for (int i = 0; i < slices; ++i) s += ll_partial[(size_t)win * slices + i];
+    r[Pp] = s;
+  } else if (p < Pp + 4) {
+    r[p] = 0.0;
+  }
+}
+
+cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices, int P,
+                                   int Pp, double* red, int windows, cudaStream_t st) {
+  dim3 grid((Pp + 4 + 255) / 256, windows);
+  reduce_partials_kernel<<<grid, 256, 0, st>>>(partial, ll_partial, slices, P, Pp, red);
+  return cudaGetLastError();
+}
+
+// ---- posterior-mean prediction -------------------------------------------
+// One thread per row, samples streamed through shared memory; forward pass of
+// mcmc_step_ffma.h:225-281 in FP32 with the reference tanh.
+template <int H>
+__global__ void __launch_bounds__(128) predict_kernel(const float* __restrict__ xs, long long n,
+                                                      const float* __restrict__ samples, int count,
+                                                      int P, float* __restrict__ out) {
+  constexpr int D = 22;
+  extern __shared__ float sw[];  // one sample
+  const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  float x[D];
+#pragma unroll
+  for (int k = 0; k < D; ++k) x[k] = r < n ? xs[r * D + k] : 0.f;
+  double acc = 0.0;
+  for (int s = 0; s < count; ++s) {
+    __syncthreads();
+    for (int p = threadIdx.x; p < P; p += blockDim.x) sw[p] = samples[(size_t)s * P + p];
+    __syncthreads();
+    float pred = sw[D * H + 2 * H];
+    for (int j = 0; j < H; ++j) {
+      float z = sw[D * H + j];
+#pragma unroll
+      for (int k = 0; k < D; ++k) z = fmaf(x[k], sw[k * H + j], z);
+      pred = fmaf(sw[D * H + H + j], tanh_ref(z), pred);
+    }
+    acc += (double)pred;
+  }
+  if (r < n) out[r] = (float)(acc / (double)count);
+}
+
+cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
+                           float* out, cudaStream_t st) {
+  const int blocks = (int)((n + 127) / 128);
+  const size_t smem = sizeof(float) * P;
+  if (H == 40) predict_kernel<40><<<blocks, 128, smem, st>>>(xs, n, samples, count, P, out);
+  else if (H == 128) predict_kernel<128><<<blocks, 128, smem, st>>>(xs, n, samples, count, P, out);
+  else return cudaErrorInvalidValue;
+  return cudaGetLastError();
+}
+
+// ---- drop-in accept ratio on caller buffers (kernel_helpers.h:153-188) ----
+// Single CTA, fixed summation order, double accumulation.
+__global__ void __launch_bounds__(1024) log_acpt_kernel(const float* __restrict__ prev_loss,
+                                                        const float* __restrict__ new_loss,
+                                                        long long n_loss,
+                                                        const float* __restrict__ prev_mom,
+                                                        const float* __restrict__ new_mom,
+                                                        const float* __restrict__ grad_cur, int P,
+                                                        float eps, float* __restrict__ out) {
+  __shared__ double dsc[32];
+  double acc = 0.0;
+  for (long long i = threadIdx.x; i < n_loss; i += blockDim.x)
+    acc += (double)new_loss[i] - (double)prev_loss[i];
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const float mf = fmaf(eps * 0.5f, grad_cur[p], new_mom[p]);
+    const float m0 = prev_mom[p];
+    acc += 0.5 * ((double)m0 * (double)m0 - (double)mf * (double)mf);
+  }
+  const double t = block_sum_f64(acc, dsc);
+  if (threadIdx.x == 0) *out = (float)t;
+}
+
+cudaError_t launch_log_acpt(const float* prev_loss, const float* new_loss, long long n_loss,
+                            const float* prev_mom, const float* new_mom, const float* grad_cur, int P,
+                            float eps, float* out, cudaStream_t st) {
+  log_acpt_kernel<<<1, 1024, 0, st>>>(prev_loss, new_loss, n_loss, prev_mom, new_mom, grad_cur, P,
+                                      eps, out);
+  return cudaGetLastError();
+}
+
+}  // namespace mcmc_b200

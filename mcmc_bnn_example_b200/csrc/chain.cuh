@@ -1,0 +1,77 @@
+// Launch parameter block of the accept kernel and the host-callable launchers
+// shared between the translation units of the library.
+#pragma once
+#include "common.cuh"
+
+namespace mcmc_b200 {
+
+enum AcceptMode : int {
+  ACC_BOOTSTRAP = 0,  // adopt the evaluated state as the chain's current state (main.h:191-202)
+  ACC_ITERATE = 1,    // accept ratio, accept/reject, adaptation, store, next momentum
+  ACC_FINALIZE = 2    // only assemble gradient and log-density sums for the caller
+};
+
+struct AcceptParams {
+  int mode;
+  int P, Pp;
+  int slices;
+  const float* partial;      // [windows][slices][Pp] of the last gradient launch
+  const double* ll_partial;  // [windows][slices]
+  const double* red_in;      // row sharding: [windows][Pp + 4] all-reduced sums, else null
+  const float* w_new;        // [windows][Pp] proposal position
+  const float* m_new;        // [windows][Pp] proposal momentum (before the closing half kick)
+  float* m0;                 // [windows][Pp] momentum drawn for the running iteration
+  float* w_cur;              // [windows][Pp] chain state
+  float* g_cur;              // [windows][Pp] full gradient at the chain state
+  double* ll_cur;            // [windows]
+  double* lp_cur;            // [windows]
+  float* eps;                // [windows]
+  int* iter;                 // [windows]
+  int* n_accept;             // [windows]
+  const long long* gwin;     // [windows] global window ids (random-stream keys)
+  float* w_start;            // [windows][Pp] where the next iteration starts from
+  float* m_start;            // [windows][Pp]
+  float* samples;            // [windows][sample_capacity][P]
+  int sample_capacity;
+  int burn_in;
+  int adapt_steps;
+  float log_target, dec_adj, inc_adj;
+  unsigned long long seed;
+  // trace of the first trace_iters iterations
+  int trace_iters;
+  float* tr_mom;             // [windows][trace_iters][P]
+  float* tr_log_u;           // [windows][trace_iters]
+  double* tr_log_acpt;
+  int* tr_accept;
+  float* tr_eps;
+  PriorParams prior;
+  // ACC_FINALIZE outputs (single window)
+  float* g_out;              // [P]
+  float* prior_loss_out;     // optional [P]
+  double* scalars_out;       // [2]: loglik, logprior
+};
+
+cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st);
+cudaError_t launch_repack(const float* x, const float* y, float* out, long long n_rows,
+                          long long rows_pad, int D, cudaStream_t st);
+cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices, int P,
+                                   int Pp, double* red, int windows, cudaStream_t st);
+cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
+                           float* out, cudaStream_t st);
+cudaError_t launch_log_acpt(const float* prev_loss, const float* new_loss, long long n_loss,
+                            const float* prev_mom, const float* new_mom, const float* grad_cur, int P,
+                            float eps, float* out, cudaStream_t st);
+
+// gradient kernels
+cudaError_t launch_grad_fp32(int H, const GradParams& g, int slices, int windows, cudaStream_t st);
+int fp32_max_ctas_per_sm(int H);
+int fp32_tile_rows(int H);
+
+// TF32 (tcgen05) path; `tmap` is a CUtensorMap over the repacked dataset
+cudaError_t launch_grad_tf32(int H, const void* tmap, const GradParams& g, int slices, int windows,
+                             float* dbg, cudaStream_t st);
+int tf32_max_ctas_per_sm(int H);
+int tf32_supported(int H);
+constexpr int TF32_TILE = 128;
+
+}  // namespace mcmc_b200

@@ -1,0 +1,199 @@
+// Shared device-side definitions of the HMC hot path: launch parameter
+// blocks, the fused leapfrog prologue, likelihood terms and the PTX wrappers
+// (mbarrier, bulk copies, tcgen05) used by the gradient kernels.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace mcmc_b200 {
+
+// Rows of the repacked dataset: 22 features, a constant 1 (so that the hidden
+// bias is row 22 of W0 and db0 is row 22 of dW0), and the target y.
+constexpr int KP = 24;          // floats per repacked row (96 bytes)
+constexpr int COL_ONE = 22;
+constexpr int COL_Y = 23;
+constexpr int MAX_SLICES = 1024;
+
+enum GradMode : int {
+  MODE_EVAL = 0,   // evaluate at w_in as it is (the reference's eps = 0 call, main.h:85-99)
+  MODE_FIRST = 1,  // half kick with the carried gradient, drift (MOM_CORRECTION = 2)
+  MODE_NEXT = 2    // full kick with the gradient of the previous step, drift
+};
+
+struct LikParams {
+  int kind;          // 0 Student-t, 1 Gaussian
+  float inv_scale;   // 1 / scale
+  float df;          // Student-t degrees of freedom
+  float norm;        // log-normaliser
+  float g_scale;     // (df + 1) / scale  (Student-t)  |  1 / scale (Gaussian)
+  float l_scale;     // -(df + 1) / 2     (Student-t)  |  -1/2      (Gaussian)
+  float inv_df;
+};
+
+struct PriorParams {
+  float neg_inv_s2;  // -1 / s^2   (PRIOR_SCALE_NEG_RECP2)
+  float inv_s;       // 1 / s
+  float norm;        // PRIOR_LOSS_NORMALIZATION
+};
+
+// One launch of a gradient kernel: grid = (slices, windows).
+struct GradParams {
+  // data
+  const float* xaug;        // [windows][rows_pad][KP]
+  long long window_stride;  // floats between windows in xaug
+  int data_window0;         // first data window this launch covers
+  int n_rows;               // valid rows per window
+  int n_tiles;              // rows_pad / tile rows
+  int P, Pp;                // parameters, padded to a multiple of 4
+  // state in / out ([windows][Pp], indexed by blockIdx.y)
+  const float* w_in;
+  const float* m_in;
+  float* w_out;
+  float* m_out;
+  const float* g_carried;   // MODE_FIRST
+  const float* partial_in;  // MODE_NEXT: [windows][slices_in][Pp] likelihood-gradient partials
+  int slices_in;
+  const double* red_in;     // MODE_NEXT with row sharding: [windows][Pp + 4] all-reduced sums
+  float* partial_out;       // [windows][slices][Pp]
+  double* ll_out;           // [windows][slices]
+  const float* eps;         // [windows] or null
+  float eps_scalar;
+  int mode;
+  float* row_loss;          // optional [windows][rows_pad]
+  long long row_loss_stride;
+  LikParams lik;
+  PriorParams prior;
+  int* status;              // device error word (bounded waits that ran out)
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+// ---- reference tanh (kernel_helpers.h:32-44): 2*sigmoid(2x)-1 on ex2/rcp
+// approximations, identity below the cut-off -------------------------------
+__device__ __forceinline__ float tanh_ref(float x) {
+  float e, d, s;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * -2.88539008177792681472f));
+  asm("add.ftz.f32 %0, %1, %2;" : "=f"(d) : "f"(1.f), "f"(e));
+  asm("rcp.approx.f32 %0, %1;" : "=f"(s) : "f"(d));
+  return fabsf(x) < 0.0048176045529544353485f ? x : fmaf(s, 2.f, -1.f);
+}
+// one MUFU op; absolute error about 5e-4, inside the TF32 mode's tolerance
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// per-row log-likelihood and d(log-lik)/d(prediction)
+// (mcmc_step_ffma.h:289-301 for Student-t)
+__device__ __forceinline__ void lik_terms(const LikParams& lk, float y, float pred, float& loss,
+                                          float& dy) {
+  float d = (y - pred) * lk.inv_scale;
+  float d2 = d * d;
+  if (lk.kind == 0) {
+    loss = lk.l_scale * log1pf(d2 * lk.inv_df) - lk.norm;
+    dy = __fdividef(d * lk.g_scale, d2 + lk.df);
+  } else {
+    loss = fmaf(lk.l_scale, d2, -lk.norm);
+    dy = d * lk.g_scale;
+  }
+}
+
+// Fused leapfrog update for parameter p of window `win`
+// (apply_leapfrog_step, mcmc_step_ffma.h:106-120; load_weights_bias :122-152):
+// every CTA of the window recomputes the same value from the same inputs in
+// the same order, slice 0 stores it.
+__device__ __forceinline__ float leapfrog_param(const GradParams& g, int win, int p, bool store) {
+  const size_t o = (size_t)win * g.Pp + p;
+  float w = g.w_in[o];
+  if (g.mode == MODE_EVAL) return w;
+  float grad;
+  float kick;
+  if (g.mode == MODE_FIRST) {
+    grad = g.g_carried[o];
+    kick = 0.5f;
+  } else {
+    if (g.red_in) {
+      grad = (float)g.red_in[(size_t)win * (g.Pp + 4) + p];
+    } else {
+      const float* pi = g.partial_in + (size_t)win * g.slices_in * g.Pp + p;
+      grad = 0.f;
+      for (int s = 0; s < g.slices_in; ++s) grad += pi[(size_t)s * g.Pp];
+    }
+    grad = fmaf(w, g.prior.neg_inv_s2, grad);  // prior gradient at the previous point
+    kick = 1.f;
+  }
+  const float eps = g.eps ? g.eps[win] : g.eps_scalar;
+  float m = g.m_in[o];
+  m = fmaf(eps * kick, grad, m);
+  w = fmaf(eps, m, w);
+  if (store) {
+    g.w_out[o] = w;
+    g.m_out[o] = m;
+  }
+  return w;
+}
+
+// ---- mbarrier / bulk-copy wrappers --------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after ~2^22 polls (well over a second), records the
+// code in the status word and returns false; the kernel then finishes with
+// whatever it has, so a lost copy can never hang the GPU.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < (1u << 22); ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 64) __nanosleep(32);
+  }
+  if (status) atomicExch(status, code);
+  return false;
+}
+// contiguous global -> shared copy through the bulk-copy engine
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes,
+                                         uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(dst_smem)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// block-wide sum of doubles in a fixed order (deterministic); blockDim.x <= 1024
+__device__ __forceinline__ double block_sum_f64(double v, double* scratch /* >= 32 */) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) scratch[w] = v;
+  __syncthreads();
+  double t = 0.0;
+  const int nw = (blockDim.x + 31) >> 5;
+  for (int i = 0; i < nw; ++i) t += scratch[i];
+  return t;
+}
+
+}  // namespace mcmc_b200

@@ -1,0 +1,89 @@
+"""CPU-only checks of the product library: it loads, exports everything the
+header declares, fails loudly without a GPU, and its host-side pieces (Philox
+streams, synthetic window generator) behave."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared():
+    hdr = open(os.path.join(ROOT, "include", "mcmc_b200.h")).read()
+    hdr = re.sub(r"/\*.*?\*/", "", hdr, flags=re.S)
+    return sorted(set(re.findall(r"\b(mcmc_b200_[a-z0-9_]+)\s*\(", hdr)))
+
+
+def test_library_exports_every_declared_symbol(built):
+    m, _ = built
+    lib = C.CDLL(m.LIB_PATH)
+    names = _declared()
+    assert len(names) >= 28
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+    assert set(m.EXPORTS) == set(names)
+
+
+def test_config_presets_match_reference_constants(built):
+    m, _ = built
+    # include/mcmc/global_params.h:27-58
+    r = m.reference_config()
+    assert (r.D, r.H, r.likelihood, r.leapfrog_steps, r.burn_in, r.adapt_steps, r.sample_capacity) == \
+        (22, 40, m.LIK_STUDENT_T, 1000, 100, 100, 800)
+    assert (r.lik_scale, r.lik_df, r.prior_scale, r.eps0, r.target_rate, r.decrement, r.increment) == \
+        (100.0, 2.2, 200.0, 0.01, 0.2, 0.1, 0.01)
+    b = m.baseline_config()
+    assert (b.likelihood, b.lik_scale, b.prior_scale, b.leapfrog_steps, b.eps0) == \
+        (m.LIK_GAUSSIAN, 1.0, 1.0, 10, 1e-3)
+
+
+def test_no_gpu_means_a_loud_error_not_a_fallback(built):
+    m, _ = built
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    with pytest.raises(m.McmcError) as e:
+        m.Context(m.baseline_config(), n_windows=1, rows=128)
+    assert "no CPU path" in str(e.value)
+
+
+def test_philox_known_answers(built):
+    m, _ = built
+    # Philox4x32-10 known-answer vectors of the Random123 distribution (kat_vectors)
+    assert m.philox_raw([0, 0, 0, 0], [0, 0]) == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    assert m.philox_raw([0xffffffff] * 4, [0xffffffff] * 2) == \
+        [0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd]
+    assert m.philox_raw([0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344], [0xa4093822, 0x299f31d0]) == \
+        [0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1]
+
+
+def test_philox_normal_stream_statistics(built):
+    m, _ = built
+    f = m.lib().mcmc_b200_philox_normal
+    v = np.array([f(123, 5, 9, 0, i) for i in range(20000)])
+    assert abs(v.mean()) < 0.03 and abs(v.std() - 1) < 0.03
+    assert abs(np.mean(v ** 3)) < 0.1 and abs(np.mean(v ** 4) - 3) < 0.25
+    # keyed by window / iteration / stream
+    assert f(123, 5, 9, 0, 0) != f(123, 6, 9, 0, 0) != f(123, 5, 10, 0, 0)
+    assert f(123, 5, 9, 0, 7) == f(123, 5, 9, 0, 7)
+
+
+def test_synthetic_window_is_deterministic_and_teacher_consistent(built):
+    m, O = built
+    x, y, t = m.synth_window(42, 3, 5000)
+    x2, y2, t2 = m.synth_window(42, 3, 5000)
+    assert np.array_equal(x, x2) and np.array_equal(y, y2) and np.array_equal(t, t2)
+    xo, _, _ = m.synth_window(42, 4, 5000)
+    assert not np.array_equal(x, xo)
+    # a prefix of the same window is the same data (index-keyed streams)
+    xp, yp, _ = m.synth_window(42, 3, 1000)
+    assert np.array_equal(xp, x[:1000]) and np.array_equal(yp, y[:1000])
+    assert abs(x.mean()) < 0.02 and abs(x.std() - 1) < 0.02
+    assert abs(t.std() - 0.3) < 0.03
+    # y = teacher(x) + N(0, 0.05^2)
+    pred = O.predict_mean(O.baseline_model(), x, t[None, :])
+    resid = y - pred
+    assert abs(resid.std() - 0.05) < 0.005 and abs(resid.mean()) < 0.005

@@ -1,0 +1,251 @@
+"""Parity of the CUDA path (through the C-ABI) with the CPU oracle on the same
+seeded inputs.  Tolerances are the ones the task states: per-call potential and
+gradient within rel 1e-5 (FP32) / 2e-3 (TF32), identical accept decisions over
+the first 50 iterations, posterior-mean predictions over 800 samples within 1 %."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+D, H, P = 22, 40, 961
+TOL = {0: 1e-5, 1: 2e-3}
+
+
+def _w(seed, scale=0.15, p=P):
+    return (scale * np.random.default_rng(seed).standard_normal(p)).astype(np.float32)
+
+
+def _presets(m, O, prec):
+    tf = prec == m.PREC_TF32
+    return {
+        "baseline": (m.baseline_config(precision=prec), O.baseline_model(tf32=tf)),
+        "reference": (m.reference_config(precision=prec), O.reference_model(tf32=tf)),
+    }
+
+
+def _grad_err(got, ref):
+    return float(np.abs(got - ref).max() / np.abs(ref).max())
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("preset", ["baseline", "reference"])
+@pytest.mark.parametrize("rows", [1, 2, 127, 129, 1000, 58368])
+def test_potential_and_grad(built, prec, preset, rows):
+    m, O = built
+    cfg, model = _presets(m, O, prec)[preset]
+    x, y, _ = m.synth_window(11, rows % 7, rows)
+    if preset == "reference":
+        x = x * np.float32(0.05)  # keep tanh out of saturation with wider weights
+    w = _w(rows, 0.3 if preset == "reference" else 0.15)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    got = ctx.potential_and_grad(0, w, want_row_loss=True)
+    ref = O.logp_grad(model, x, y, w, want_losses=True)
+    tol = TOL[prec]
+    assert _grad_err(got["grad"], ref["grad"]) < tol
+    assert abs(got["loglik"] - ref["loglik"]) <= tol * abs(ref["loglik"])
+    assert abs(got["logprior"] - ref["logprior"]) <= 1e-6 * abs(ref["logprior"])
+    assert np.allclose(got["row_loss"], ref["row_loss"], rtol=10 * tol, atol=10 * tol)
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_tf32_and_fp32_modes_agree_with_exact_oracle(built, prec):
+    """Both modes against the untruncated oracle: FP32 at 1e-5, TF32 at 2e-3."""
+    m, O = built
+    rows = 20000
+    x, y, _ = m.synth_window(5, 1, rows)
+    w = _w(77)
+    ctx = m.Context(m.baseline_config(precision=prec), n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    got = ctx.potential_and_grad(0, w)
+    ref = O.logp_grad(O.baseline_model(tf32=False), x, y, w)
+    assert _grad_err(got["grad"], ref["grad"]) < TOL[prec]
+    assert abs(got["loglik"] - ref["loglik"]) <= TOL[prec] * abs(ref["loglik"])
+    ctx.close()
+
+
+def test_fp32_wide_model(built):
+    m, O = built
+    rows, Hw = 3000, 128
+    Pw = 22 * Hw + 2 * Hw + 1
+    x, y, _ = m.synth_window(3, 0, rows, H=Hw)
+    w = _w(5, 0.1, Pw)
+    ctx = m.Context(m.baseline_config(H=Hw), n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    got = ctx.potential_and_grad(0, w)
+    ref = O.logp_grad(O.baseline_model(H=Hw), x, y, w)
+    assert _grad_err(got["grad"], ref["grad"]) < 1e-5
+    assert abs(got["loglik"] - ref["loglik"]) <= 1e-5 * abs(ref["loglik"])
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("L", [1, 2, 10])
+def test_leapfrog_matches_oracle_mcmc_step(built, prec, L):
+    m, O = built
+    rows = 5000
+    x, y, _ = m.synth_window(21, 2, rows)
+    cfg, model = _presets(m, O, prec)["baseline"]
+    w0 = _w(1)
+    mom = np.random.default_rng(2).standard_normal(P).astype(np.float32)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    g0 = ctx.potential_and_grad(0, w0)["grad"]
+    got = ctx.leapfrog(0, L, 1e-3, w0, mom, g0)
+    ref = O.mcmc_step(model, x, y, L, 1e-3, w0, mom, g0)
+    tol = TOL[prec]
+    assert np.allclose(got["w_next"], ref["w_next"], rtol=tol, atol=tol * 1e-2)
+    assert np.allclose(got["mom_next"], ref["mom_next"], rtol=tol, atol=tol)
+    assert _grad_err(got["grad_cur"], ref["grad_cur"]) < tol
+    assert abs(got["loglik"] - ref["loglik"]) <= tol * abs(ref["loglik"])
+    ctx.close()
+
+
+@pytest.mark.parametrize("preset", ["baseline", "reference"])
+def test_accept_decisions_identical_over_first_50_iterations(built, preset):
+    """The device chain replayed on the CPU with the draws the device used."""
+    m, O = built
+    rows, n_iter = 58368 if preset == "baseline" else 8192, 50
+    x, y, _ = m.synth_window(9, 0, rows)
+    if preset == "baseline":
+        cfg = m.baseline_config(sample_capacity=n_iter, trace_iters=n_iter, seed=1234)
+        model, sampler = O.baseline_model(), O.baseline_sampler()
+    else:
+        # the reference's Student-t / N(0,200^2) preset with its adaptive burn-in, shortened to
+        # L = 10 so that the CPU replay finishes in seconds; eps0 = 0.2 gives accepts, rejections and both
+        # branches of the step-size adaptation within 50 iterations
+        cfg = m.reference_config(leapfrog_steps=10, burn_in=0, adapt_steps=30, sample_capacity=n_iter,
+                                 trace_iters=n_iter, seed=99, eps0=0.2)
+        x = x * np.float32(0.05)
+        model, sampler = O.reference_model(), O.Sampler(10, 30, 0.2, 0.2, 0.1, 0.01)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    ctx.run_chain(n_iter)
+    tr = ctx.get_trace(0)
+    samples = ctx.get_samples(0, 0, n_iter)
+    ref = O.hmc_chain(model, sampler, x, y, tr["momenta"], tr["log_u"])
+    assert np.array_equal(tr["accepted"], ref["accepted"])
+    assert np.allclose(tr["eps"], ref["eps"], rtol=1e-6)
+    assert np.allclose(tr["log_acpt"], ref["log_acpt"], rtol=1e-3, atol=2e-2)
+    assert np.allclose(samples, ref["samples"], rtol=1e-4, atol=1e-5)
+    info = ctx.chain_info(0)
+    assert info["iterations"] == n_iter and info["accepted"] == int(ref["accepted"].sum())
+    if preset == "reference":
+        assert 0 < ref["accepted"].sum() < n_iter  # the case exercises both branches
+    # draws are N(0,1) / log U(0,1]
+    assert abs(tr["momenta"].std() - 1) < 0.02 and np.all(tr["log_u"] <= 0)
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_posterior_mean_prediction_over_800_samples(built, prec):
+    m, O = built
+    rows, n_iter = 2048, 800
+    x, y, _ = m.synth_window(31, 0, rows)
+    cfg = m.baseline_config(precision=prec, sample_capacity=n_iter, trace_iters=n_iter, seed=5,
+                            eps0=2e-3)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    ctx.set_window_data(0, x, y)
+    ctx.run_chain(n_iter)
+    tr = ctx.get_trace(0)
+    ref = O.hmc_chain(O.baseline_model(), O.baseline_sampler(eps=2e-3), x, y, tr["momenta"], tr["log_u"])
+    xs, _, _ = m.synth_window(31, 1, 512)
+    got = ctx.predict_mean(0, xs)
+    exp = O.predict_mean(O.baseline_model(), xs, ref["samples"])
+    rel_l2 = np.linalg.norm(got - exp) / np.linalg.norm(exp)
+    assert rel_l2 < 1e-2
+    # and the device's own forward pass over its own samples is exact to FP32
+    own = O.predict_mean(O.baseline_model(), xs, ctx.get_samples(0))
+    assert np.linalg.norm(got - own) / np.linalg.norm(own) < 1e-5
+    ll, lp = ctx.final_loss(0, 0, 16)
+    ell, elp = O.final_loss(O.baseline_model(tf32=bool(prec)), x, y, ctx.get_samples(0, 0, 16))
+    assert abs(ll - ell) <= TOL[prec] * abs(ell) and abs(lp - elp) <= 1e-5 * abs(elp)
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_batched_windows_equal_single_window_chains_bitwise(built, prec):
+    """Windows are independent: a window gives the same chain alone or batched,
+    wherever it sits (the random streams are keyed by the global window id)."""
+    m, _ = built
+    rows, n_iter, W = 3000, 12, 3
+    data = [m.synth_window(8, g, rows) for g in (10, 11, 12)]
+    cfg = m.baseline_config(precision=prec, sample_capacity=n_iter, slices=5, seed=3)
+    batched = m.Context(cfg, n_windows=W, rows=rows)
+    for i, (x, y, _) in enumerate(data):
+        batched.set_window_data(i, x, y, global_window=10 + i)
+    batched.run_chain(n_iter)
+    for i, (x, y, _) in enumerate(data):
+        single = m.Context(cfg, n_windows=1, rows=rows)
+        single.set_window_data(0, x, y, global_window=10 + i)
+        single.run_chain(5)
+        single.run_chain(n_iter - 5)  # split runs continue the same chain
+        assert np.array_equal(single.get_samples(0), batched.get_samples(i))
+        single.close()
+    # and a second identical run is bit-identical (no atomics anywhere)
+    again = m.Context(cfg, n_windows=W, rows=rows)
+    for i, (x, y, _) in enumerate(data):
+        again.set_window_data(i, x, y, global_window=10 + i)
+    again.run_chain(n_iter)
+    for i in range(W):
+        assert np.array_equal(again.get_samples(i), batched.get_samples(i))
+    assert not np.array_equal(batched.get_samples(0), batched.get_samples(1))
+    again.close()
+    batched.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_mcmc_step_and_log_acpt_drop_ins_on_device_buffers(built, prec):
+    """mcmc::mcmc_step / mcmc::log_acpt_prec semantics on caller-owned device buffers."""
+    import torch
+    m, O = built
+    rows, L, eps = 4096, 3, 2e-3
+    x, y, _ = m.synth_window(2, 0, rows)
+    cfg, model = _presets(m, O, prec)["baseline"]
+    dev = torch.device("cuda:0")
+    tx, ty = torch.from_numpy(x).to(dev), torch.from_numpy(y).to(dev)
+    w0 = _w(3)
+    mom = np.random.default_rng(4).standard_normal(P).astype(np.float32)
+    ref0 = O.logp_grad(model, x, y, w0, want_losses=True)
+    g0 = ref0["grad"].astype(np.float32)
+    t = {k: torch.from_numpy(v).to(dev) for k, v in dict(wp=w0, mp=mom, gp=g0).items()}
+    out = {k: torch.full((P,), 7.0, device=dev) for k in ("wn", "mn", "gc", "gn")}
+    loss = torch.zeros(rows + P, device=dev)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    s = torch.cuda.current_stream().cuda_stream
+    for _ in range(2):  # second call reuses the repacked dataset
+        ctx.mcmc_step(tx.data_ptr(), ty.data_ptr(), t["wp"].data_ptr(), out["wn"].data_ptr(),
+                      t["mp"].data_ptr(), out["mn"].data_ptr(), t["gp"].data_ptr(), out["gc"].data_ptr(),
+                      out["gn"].data_ptr(), loss.data_ptr(), L, eps, stream=s)
+    torch.cuda.synchronize()
+    ref = O.mcmc_step(model, x, y, L, eps, w0, mom, g0)
+    tol = TOL[prec]
+    assert np.allclose(out["wn"].cpu().numpy(), ref["w_next"], rtol=tol, atol=tol * 1e-2)
+    assert np.allclose(out["mn"].cpu().numpy(), ref["mom_next"], rtol=tol, atol=tol)
+    assert _grad_err(out["gc"].cpu().numpy(), ref["grad_cur"]) < tol
+    assert np.all(out["gn"].cpu().numpy() == 0)
+    assert np.allclose(loss.cpu().numpy(), ref["loss_values"], rtol=10 * tol, atol=10 * tol)
+    # accept ratio on device buffers
+    prev_loss = torch.from_numpy(np.concatenate([ref0["row_loss"], ref0["prior_loss"]])).to(dev)
+    la = ctx.log_acpt(prev_loss.data_ptr(), loss.data_ptr(), rows + P, t["mp"].data_ptr(),
+                      out["mn"].data_ptr(), out["gc"].data_ptr(), eps, stream=s)
+    mf = ref["mom_next"].astype(np.float64) + 0.5 * np.float32(eps) * ref["grad_cur"].astype(np.float64)
+    exp = float(np.sum(ref["loss_values"].astype(np.float64)) -
+                np.sum(prev_loss.cpu().numpy().astype(np.float64)) +
+                0.5 * (np.sum(mom.astype(np.float64) ** 2) - np.sum(mf ** 2)))
+    assert abs(la - exp) < max(5e-3, 20 * tol * abs(exp))
+    ctx.close()
+
+
+def test_errors_are_reported_not_fatal(built):
+    m, _ = built
+    with pytest.raises(m.McmcError):
+        m.Context(m.baseline_config(D=21), n_windows=1, rows=128)
+    ctx = m.Context(m.baseline_config(), n_windows=2, rows=256)
+    with pytest.raises(m.McmcError) as e:
+        ctx.run_chain(1)  # no data yet
+    assert "no data" in str(e.value)
+    with pytest.raises(m.McmcError):
+        ctx.get_samples(5)
+    ctx.close()
