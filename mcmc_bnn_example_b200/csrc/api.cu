@@ -94,7 +94,7 @@ struct mcmc_b200_ctx {
   // dataset
   float* xaug = nullptr;
   std::vector<char> window_set;
-  CUtensorMap tmap;
+  CUtensorMap tmap, tmap_mn;
   bool tmap_ok = false;
   // chain state
   float *wbuf[2] = {}, *mbuf[2] = {}, *w_cur = nullptr, *g_cur = nullptr, *m0 = nullptr;
@@ -218,6 +218,10 @@ static int make_tensor_map(mcmc_b200_ctx* c) {
   CUresult r = ((EncodeFn)fn)(&c->tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box,
                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS)
+    r = ((EncodeFn)fn)(&c->tmap_mn, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box, estr,
+                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
+                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char b[96];
     snprintf(b, sizeof b, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -411,7 +415,7 @@ static int launch_grad(mcmc_b200_ctx* c, const GradParams& g, int slices, int wi
                        float* dbg = nullptr) {
   cudaError_t e;
   if (c->cfg.precision == MCMC_B200_PREC_TF32)
-    e = launch_grad_tf32(c->cfg.H, &c->tmap, g, slices, windows, dbg, st);
+    e = launch_grad_tf32(c->cfg.H, &c->tmap, &c->tmap_mn, g, slices, windows, dbg, st);
   else
     e = launch_grad_fp32(c->cfg.H, g, slices, windows, st);
   c->launches++;

@@ -67,9 +67,10 @@ cudaError_t launch_grad_fp32(int H, const GradParams& g, int slices, int windows
 int fp32_max_ctas_per_sm(int H);
 int fp32_tile_rows(int H);
 
-// TF32 (tcgen05) path; `tmap` is a CUtensorMap over the repacked dataset
-cudaError_t launch_grad_tf32(int H, const void* tmap, const GradParams& g, int slices, int windows,
-                             float* dbg, cudaStream_t st);
+// TF32 (tcgen05) path; `tmap` / `tmap_mn` are CUtensorMaps over the repacked dataset that stage a
+// row tile with 16-byte-chunk and with 32-byte-chunk swizzling
+cudaError_t launch_grad_tf32(int H, const void* tmap, const void* tmap_mn, const GradParams& g, int slices,
+                             int windows, float* dbg, cudaStream_t st);
 int tf32_max_ctas_per_sm(int H);
 int tf32_supported(int H);
 constexpr int TF32_TILE = 128;

@@ -29,6 +29,8 @@
 //
 // No atomics; every wait is bounded and reports through the status word.
 #include <cuda.h>
+#include <stdio.h>
+#include <stdlib.h>
 #include "common.cuh"
 #include "chain.cuh"
 
@@ -48,12 +50,13 @@ struct Tf32Geom {
   static constexpr int BWD_COL0 = FWD_COLS;
   static constexpr int TMEM_COLS = FWD_COLS + 32 <= 128 ? 128 : 256;
   static constexpr int TILE_BYTES = TF32_TILE * 128;       // 128 rows x 32 floats (24 real + 8 zero fill)
-  static constexpr int XS_BYTES = NST * TILE_BYTES;
+  static constexpr int XS_BYTES = NST * TILE_BYTES;          // K-major copies (forward A operand)
+  static constexpr int XB_BYTES = NST * TILE_BYTES;          // MN-major copies (backward B operand)
   static constexpr int ES_BYTES = ATOMS * TILE_BYTES;
   static constexpr int W0S_BYTES = NF * 128;
   static constexpr int W1_BYTES = (H + 3) / 4 * 16;
   static constexpr int P = D * H + 2 * H + 1;
-  static constexpr size_t SMEM = 1024 + XS_BYTES + ES_BYTES + W0S_BYTES + W1_BYTES;
+  static constexpr size_t SMEM = 1024 + XS_BYTES + XB_BYTES + ES_BYTES + W0S_BYTES + W1_BYTES;
   static_assert(H % 4 == 0, "hidden width must be a multiple of 4");
   static_assert(TF32_THREADS * (H + 1) * 4 <= ES_BYTES, "dW1 reduction scratch aliases the E buffer");
 };
@@ -101,12 +104,25 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tmap, 
       : "memory");
 }
 
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), version 1.
-// Byte offsets are encoded without their 4 low bits.
+// Shared-memory matrix descriptor (version 1).  Byte offsets are encoded
+// without their 4 low bits.  Layout types used here:
+//   2 = 128-byte swizzle of 16-byte chunks   (K-major operands)
+//   1 = 128-byte swizzle of 32-byte chunks   (the only layout the tensor core
+//       accepts for MN-major operands of 32-bit types)
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes, uint32_t layout_type) {
+  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) |
+         ((uint64_t)layout_type << 61);
+}
 __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
                                                     uint32_t sbo_bytes) {
-  return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
-         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | (2ull << 61);
+  return umma_desc(smem_addr, lbo_bytes, sbo_bytes, 2);
+}
+// MN-major, 32-byte-chunk swizzle: rows (K) of 128 bytes, groups of 4 rows 512 bytes apart,
+// 32-float atoms along M/N `atom_stride` bytes apart
+__device__ __forceinline__ uint64_t umma_desc_mn32(uint32_t smem_addr, uint32_t atom_stride) {
+  return umma_desc(smem_addr, atom_stride, 512, 1);
 }
 // Instruction descriptor: F32 accumulate, TF32 x TF32, dense.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
@@ -116,7 +132,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_ma
 
 template <int H, int NST>
 __global__ void __launch_bounds__(TF32_THREADS)
-grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, float* dbg) {
+grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_mn,
+                 const GradParams g, float* dbg) {
   using G = Tf32Geom<H, NST>;
   constexpr int D = G::D, NF = G::NF, MB = G::MB, NB = G::NB;
   constexpr uint32_t IDESC_FWD = umma_idesc_tf32(128, NF, 0, 0);
@@ -126,7 +143,8 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
   unsigned char* base =
       reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* xs = base;                   // [NST][128 rows][128 B], TMA-written, swizzled
-  unsigned char* es = xs + G::XS_BYTES;       // [ATOMS][128 rows][128 B], E operand, swizzled
+  unsigned char* xb = xs + G::XS_BYTES;       // [NST][128 rows][128 B], same tiles, 32-byte-chunk swizzle
+  unsigned char* es = xb + G::XB_BYTES;       // [ATOMS][128 rows][128 B], E operand, 32-byte-chunk swizzle
   unsigned char* w0s = es + G::ES_BYTES;      // [NF][128 B] weights, K-major, swizzled
   float* w1s = reinterpret_cast<float*>(w0s + G::W0S_BYTES);
   __shared__ __align__(8) uint64_t bar_tma[NST];
@@ -169,8 +187,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
 
   if (tid == 0) {
     for (int s = 0; s < NST && t0 + s < t1; ++s) {
-      mbar_expect_tx(&bar_tma[s], G::TILE_BYTES);
+      mbar_expect_tx(&bar_tma[s], 2 * G::TILE_BYTES);
       tma_load_2d(xs + s * G::TILE_BYTES, &tmap, 0, grow0 + (t0 + s) * TF32_TILE, &bar_tma[s]);
+      tma_load_2d(xb + s * G::TILE_BYTES, &tmap_mn, 0, grow0 + (t0 + s) * TF32_TILE, &bar_tma[s]);
     }
   }
   // fused leapfrog update; W0 and b0 go into the swizzled K-major B operand:
@@ -222,8 +241,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
       const int tn = t + NST - 1;
       if (it > 0 && tn < t1 && ok) {
         const int sn = (it + NST - 1) % NST;
-        mbar_expect_tx(&bar_tma[sn], G::TILE_BYTES);
+        mbar_expect_tx(&bar_tma[sn], 2 * G::TILE_BYTES);
         tma_load_2d(xs + sn * G::TILE_BYTES, &tmap, 0, grow0 + tn * TF32_TILE, &bar_tma[sn]);
+        tma_load_2d(xb + sn * G::TILE_BYTES, &tmap_mn, 0, grow0 + tn * TF32_TILE, &bar_tma[sn]);
       }
     }
     tc_fence_after();
@@ -240,6 +260,8 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
 #pragma unroll
       for (int j = 0; j < H; ++j) dbg[tid * 64 + j] = z[j];
       dbg[tid * 64 + 63] = y;
+      for (int c = 0; c < 32; ++c)
+        dbg[12288 + tid * 32 + c] = reinterpret_cast<const float*>(xb + stage * G::TILE_BYTES)[tid * 32 + c];
     }
     float pred = b1;
 #pragma unroll
@@ -273,7 +295,8 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
     unsigned char* erow = es + tid * 128;
 #pragma unroll
     for (int c = 0; c < H / 4; ++c)
-      *reinterpret_cast<float4*>(erow + (c >> 3) * G::TILE_BYTES + (((c & 7) ^ (tid & 7)) << 4)) =
+      *reinterpret_cast<float4*>(erow + (c >> 3) * G::TILE_BYTES + ((((c & 7) >> 1) ^ (tid & 3)) << 5) +
+                                 ((c & 1) << 4)) =
           make_float4(z[4 * c], z[4 * c + 1], z[4 * c + 2], z[4 * c + 3]);
     fence_proxy_async_smem();
     tc_fence_before();
@@ -295,11 +318,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap, const GradParams g, f
         tc_commit(&bar_fwd);
         }
       }
-      const uint32_t xb = smem_u32(xs + stage * G::TILE_BYTES);
+      const uint32_t xba = smem_u32(xb + stage * G::TILE_BYTES);
 #pragma unroll
       for (int kb = 0; kb < TF32_TILE / 8; ++kb)
-        tc_mma_tf32(tmem_bwd, umma_desc_sw128(es_addr + kb * 1024, G::TILE_BYTES, 1024),
-                    umma_desc_sw128(xb + kb * 1024, G::TILE_BYTES, 1024), IDESC_BWD,
+        tc_mma_tf32(tmem_bwd, umma_desc_mn32(es_addr + kb * 1024, G::TILE_BYTES),
+                    umma_desc_mn32(xba + kb * 1024, G::TILE_BYTES), IDESC_BWD,
                     (it > 0 || kb > 0) ? 1u : 0u);
       tc_commit(&bar_bwd);
     }
@@ -368,8 +391,8 @@ constexpr int TF32_NST = 2;
 int tf32_supported(int H) { return H == 40; }
 
 template <int H>
-static cudaError_t launch_tf32_t(const void* tmap, const GradParams& g, int slices, int windows,
-                                 float* dbg, cudaStream_t st) {
+static cudaError_t launch_tf32_t(const void* tmap, const void* tmap_mn, const GradParams& g, int slices,
+                                 int windows, float* dbg, cudaStream_t st) {
   using G = Tf32Geom<H, TF32_NST>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -378,16 +401,19 @@ static cudaError_t launch_tf32_t(const void* tmap, const GradParams& g, int slic
     cudaError_t e = cudaFuncSetAttribute(grad_tf32_kernel<H, TF32_NST>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::SMEM);
     if (e != cudaSuccess) return e;
+    e = cudaFuncSetAttribute(grad_tf32_kernel<H, TF32_NST>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
   grad_tf32_kernel<H, TF32_NST><<<dim3(slices, windows), TF32_THREADS, G::SMEM, st>>>(
-      *reinterpret_cast<const CUtensorMap*>(tmap), g, dbg);
+      *reinterpret_cast<const CUtensorMap*>(tmap), *reinterpret_cast<const CUtensorMap*>(tmap_mn), g, dbg);
   return cudaGetLastError();
 }
 
-cudaError_t launch_grad_tf32(int H, const void* tmap, const GradParams& g, int slices, int windows,
-                             float* dbg, cudaStream_t st) {
-  if (H == 40) return launch_tf32_t<40>(tmap, g, slices, windows, dbg, st);
+cudaError_t launch_grad_tf32(int H, const void* tmap, const void* tmap_mn, const GradParams& g, int slices,
+                             int windows, float* dbg, cudaStream_t st) {
+  if (H == 40) return launch_tf32_t<40>(tmap, tmap_mn, g, slices, windows, dbg, st);
   return cudaErrorInvalidValue;
 }
 
@@ -395,10 +421,14 @@ int tf32_max_ctas_per_sm(int H) {
   int n = 0;
   if (H == 40) {
     using G = Tf32Geom<40, TF32_NST>;
-    cudaFuncSetAttribute(grad_tf32_kernel<40, TF32_NST>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)G::SMEM);
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, grad_tf32_kernel<40, TF32_NST>, TF32_THREADS,
-                                                  G::SMEM);
+    cudaError_t e1 = cudaFuncSetAttribute(grad_tf32_kernel<40, TF32_NST>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::SMEM);
+    cudaFuncSetAttribute(grad_tf32_kernel<40, TF32_NST>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                         cudaSharedmemCarveoutMaxShared);
+    cudaError_t e2 = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, grad_tf32_kernel<40, TF32_NST>,
+                                                                   TF32_THREADS, G::SMEM);
+    if (getenv("MCMC_B200_DEBUG"))
+      fprintf(stderr, "tf32 occupancy: attr=%d occ=%d n=%d smem=%zu\n", (int)e1, (int)e2, n, (size_t)G::SMEM);
     const int by_tmem = 512 / G::TMEM_COLS;
     if (n > by_tmem) n = by_tmem;
   }
@@ -406,3 +436,18 @@ int tf32_max_ctas_per_sm(int H) {
 }
 
 }  // namespace mcmc_b200
+
+extern "C" __attribute__((visibility("default"))) void mcmc_b200_debug_occupancy() {
+  using namespace mcmc_b200;
+  cudaFuncAttributes a;
+  cudaFuncGetAttributes(&a, grad_tf32_kernel<40, TF32_NST>);
+  printf("tf32 kernel: regs %d static smem %zu maxDyn %d local %zu maxThreads %d carve %d\n", a.numRegs,
+         a.sharedSizeBytes, a.maxDynamicSharedSizeBytes, a.localSizeBytes, a.maxThreadsPerBlock,
+         a.preferredShmemCarveout);
+  for (int kb = 8; kb <= 112; kb += 8) {
+    int n = -1;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, grad_tf32_kernel<40, TF32_NST>, 128,
+                                                                  (size_t)kb * 1024);
+    printf("  dyn smem %d KB -> %d CTAs/SM (err %d)\n", kb, n, (int)e);
+  }
+}

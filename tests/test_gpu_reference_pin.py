@@ -55,12 +55,12 @@ def test_oracle_and_cuda_path_against_reference_kernel(built):
     assert np.array_equal(r1["w_next"], w)
 
     # (2) ten leapfrog steps: mcmc_step<T,10>
-    eps = 5.0
+    eps = 0.2
     g0 = o1["grad"].astype(np.float32)
     r10 = _ref_step(ref, x, y, 10, eps, w, mom, g0)
     o10 = O.mcmc_step(model, x, y, 10, eps, w, mom, g0)
-    assert np.allclose(r10["w_next"], o10["w_next"], rtol=1e-5, atol=1e-6)
-    assert np.allclose(r10["mom_next"], o10["mom_next"], rtol=1e-5, atol=1e-5)
+    assert np.abs(r10["w_next"] - o10["w_next"]).max() < 1e-5 * np.abs(o10["w_next"]).max()
+    assert np.abs(r10["mom_next"] - o10["mom_next"]).max() < 1e-5 * np.abs(o10["mom_next"]).max()
     assert np.abs(r10["grad_cur"] - o10["grad_cur"]).max() < 1e-5 * np.abs(o10["grad_cur"]).max()
     assert np.allclose(r10["loss_values"], o10["loss_values"], rtol=1e-5, atol=1e-5)
 
@@ -82,7 +82,8 @@ def test_oracle_and_cuda_path_against_reference_kernel(built):
     assert np.abs(mine["grad"] - r1["grad_cur"]).max() < 1e-5 * gscale
     assert np.allclose(mine["row_loss"], r1["loss_values"][:N], rtol=1e-5, atol=1e-5)
     lf = ctx.leapfrog(0, 10, eps, w, mom, g0)
-    assert np.allclose(lf["w_next"], r10["w_next"], rtol=1e-5, atol=1e-6)
+    assert np.abs(lf["w_next"] - r10["w_next"]).max() < 1e-5 * np.abs(r10["w_next"]).max()
+    assert np.abs(lf["mom_next"] - r10["mom_next"]).max() < 1e-5 * np.abs(r10["mom_next"]).max()
     assert np.abs(lf["grad_cur"] - r10["grad_cur"]).max() < 1e-5 * np.abs(r10["grad_cur"]).max()
     ctx.close()
 
