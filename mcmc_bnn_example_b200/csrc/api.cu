@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <algorithm>
 #include <string>
 #include <vector>
 
@@ -94,8 +95,12 @@ struct mcmc_b200_ctx {
   // dataset
   float* xaug = nullptr;
   std::vector<char> window_set;
-  CUtensorMap tmap, tmap_mn;
+  CUtensorMap tmap_mn;
   bool tmap_ok = false;
+  // persistent (TF32) kernel work tables: chain launches and single-window launches
+  int *tab_seg_ptr = nullptr, *tab_nslot = nullptr, *xtab_seg_ptr = nullptr, *xtab_nslot = nullptr;
+  int4 *tab_segs = nullptr, *xtab_segs = nullptr;
+  int tab_ctas = 0, xtab_ctas = 0;
   // chain state
   float *wbuf[2] = {}, *mbuf[2] = {}, *w_cur = nullptr, *g_cur = nullptr, *m0 = nullptr;
   float* partial[2] = {};
@@ -215,13 +220,10 @@ static int make_tensor_map(mcmc_b200_ctx* c) {
   cuuint64_t gstride[1] = {(cuuint64_t)(KP * sizeof(float))};
   cuuint32_t box[2] = {32, (cuuint32_t)TF32_TILE};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = ((EncodeFn)fn)(&c->tmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box,
-                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  // 32-byte-chunk swizzle: the layout the tensor core wants for MN-major TF32 operands
+  CUresult r = ((EncodeFn)fn)(&c->tmap_mn, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box,
+                              estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r == CUDA_SUCCESS)
-    r = ((EncodeFn)fn)(&c->tmap_mn, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, c->xaug, gdim, gstride, box, estr,
-                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B,
-                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     char b[96];
     snprintf(b, sizeof b, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
@@ -230,6 +232,11 @@ static int make_tensor_map(mcmc_b200_ctx* c) {
   c->tmap_ok = true;
   return MCMC_B200_OK;
 }
+
+// Cuts the flattened (window, tile) list of a launch into one contiguous range per CTA and each
+// range into per-window segments; slot = the segment's index among its window's segments.
+static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
+                            int** d_seg_ptr, int4** d_segs, int** d_nslot, int* n_ctas, int* max_slots);
 
 API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows, int64_t rows,
                          mcmc_b200_ctx** out) {
@@ -263,24 +270,35 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   c->num_sms = prop.multiProcessorCount;
   const bool tf32 = cfg->precision == MCMC_B200_PREC_TF32;
   c->tile_rows = tf32 ? TF32_TILE : fp32_tile_rows(cfg->H);
-  c->ctas_per_sm = tf32 ? tf32_max_ctas_per_sm(cfg->H) : fp32_max_ctas_per_sm(cfg->H);
+  c->ctas_per_sm = tf32 ? 1 : fp32_max_ctas_per_sm(cfg->H);
   if (c->ctas_per_sm < 1) c->ctas_per_sm = 1;
   const long long n_tiles = c->rows_pad / c->tile_rows;
-  const long long capacity = (long long)c->num_sms * c->ctas_per_sm;
-  long long s = cfg->slices > 0 ? cfg->slices : capacity / n_windows;
-  if (s < 1) s = 1;
-  if (s > n_tiles) s = n_tiles;
-  if (s > MAX_SLICES) s = MAX_SLICES;
-  c->slices = (int)s;
-  long long sx = cfg->slices > 0 ? cfg->slices : capacity;
-  if (sx > n_tiles) sx = n_tiles;
-  if (sx > MAX_SLICES) sx = MAX_SLICES;
-  if (sx < 1) sx = 1;
-  c->slices_x = (int)sx;
   c->window_set.assign(n_windows, 0);
   c->h_gwin.assign(n_windows, 0);
   cudaError_t es = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
   if (es != cudaSuccess) { delete c; return fail(MCMC_B200_ERR_CUDA, "cudaStreamCreate failed"); }
+  if (tf32) {
+    // persistent kernel: cfg.slices, when given, is the number of CTAs of a launch
+    const int max_ctas = cfg->slices > 0 ? cfg->slices : c->num_sms;
+    int r_ = build_work_table(c, n_windows, n_tiles, max_ctas, &c->tab_seg_ptr, &c->tab_segs, &c->tab_nslot,
+                              &c->tab_ctas, &c->slices);
+    if (r_ == MCMC_B200_OK)
+      r_ = build_work_table(c, 1, n_tiles, max_ctas, &c->xtab_seg_ptr, &c->xtab_segs, &c->xtab_nslot,
+                            &c->xtab_ctas, &c->slices_x);
+    if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
+  } else {
+    const long long capacity = (long long)c->num_sms * c->ctas_per_sm;
+    long long s = cfg->slices > 0 ? cfg->slices : capacity / n_windows;
+    if (s < 1) s = 1;
+    if (s > n_tiles) s = n_tiles;
+    if (s > MAX_SLICES) s = MAX_SLICES;
+    c->slices = (int)s;
+    long long sx = cfg->slices > 0 ? cfg->slices : capacity;
+    if (sx > n_tiles) sx = n_tiles;
+    if (sx > MAX_SLICES) sx = MAX_SLICES;
+    if (sx < 1) sx = 1;
+    c->slices_x = (int)sx;
+  }
 
   const size_t W = n_windows, Pp = c->Pp, P = c->P;
   DA(c->xaug, W * c->rows_pad * KP * sizeof(float));
@@ -331,6 +349,41 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   std::vector<float> e(W, (float)cfg->eps0);
   cudaMemcpy(c->eps, e.data(), W * 4, cudaMemcpyHostToDevice);
   *out = c;
+  return MCMC_B200_OK;
+}
+
+static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
+                            int** d_seg_ptr, int4** d_segs, int** d_nslot, int* n_ctas, int* max_slots) {
+  const long long T = (long long)windows * tiles_per_window;
+  long long G = max_ctas;
+  if (G > T) G = T;
+  if (G < 1) G = 1;
+  std::vector<int> seg_ptr(G + 1, 0), nslot(windows, 0);
+  std::vector<int4> segs;
+  for (long long b = 0; b < G; ++b) {
+    long long s = b * T / G;
+    const long long e = (b + 1) * T / G;
+    seg_ptr[b] = (int)segs.size();
+    while (s < e) {
+      const long long w = s / tiles_per_window;
+      const long long wend = std::min(e, (w + 1) * tiles_per_window);
+      segs.push_back(make_int4((int)w, (int)(s - w * tiles_per_window), (int)(wend - w * tiles_per_window),
+                               nslot[w]++));
+      s = wend;
+    }
+  }
+  seg_ptr[G] = (int)segs.size();
+  int ms = 1;
+  for (int w = 0; w < windows; ++w) ms = std::max(ms, nslot[w]);
+  int r = dalloc(c, (void**)d_seg_ptr, seg_ptr.size() * sizeof(int), false);
+  if (r == MCMC_B200_OK) r = dalloc(c, (void**)d_segs, segs.size() * sizeof(int4), false);
+  if (r == MCMC_B200_OK) r = dalloc(c, (void**)d_nslot, nslot.size() * sizeof(int), false);
+  if (r != MCMC_B200_OK) return r;
+  CK(cudaMemcpy(*d_seg_ptr, seg_ptr.data(), seg_ptr.size() * sizeof(int), cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(*d_segs, segs.data(), segs.size() * sizeof(int4), cudaMemcpyHostToDevice));
+  CK(cudaMemcpy(*d_nslot, nslot.data(), nslot.size() * sizeof(int), cudaMemcpyHostToDevice));
+  *n_ctas = (int)G;
+  *max_slots = ms;
   return MCMC_B200_OK;
 }
 
@@ -411,13 +464,20 @@ static GradParams base_grad_params(mcmc_b200_ctx* c) {
   return g;
 }
 
-static int launch_grad(mcmc_b200_ctx* c, const GradParams& g, int slices, int windows, cudaStream_t st,
-                       float* dbg = nullptr) {
+// `single` selects the single-window work table / slot count (explicit-state calls)
+static int launch_grad(mcmc_b200_ctx* c, GradParams g, bool single, cudaStream_t st, float* dbg = nullptr) {
   cudaError_t e;
-  if (c->cfg.precision == MCMC_B200_PREC_TF32)
-    e = launch_grad_tf32(c->cfg.H, &c->tmap, &c->tmap_mn, g, slices, windows, dbg, st);
-  else
-    e = launch_grad_fp32(c->cfg.H, g, slices, windows, st);
+  const int slots = single ? c->slices_x : c->slices;
+  g.slices_in = slots;
+  g.slices_out = slots;
+  if (c->cfg.precision == MCMC_B200_PREC_TF32) {
+    g.nslot_in = single ? c->xtab_nslot : c->tab_nslot;
+    g.seg_ptr = single ? c->xtab_seg_ptr : c->tab_seg_ptr;
+    g.segs = single ? c->xtab_segs : c->tab_segs;
+    e = launch_grad_tf32(c->cfg.H, &c->tmap_mn, g, single ? c->xtab_ctas : c->tab_ctas, dbg, st);
+  } else {
+    e = launch_grad_fp32(c->cfg.H, g, slots, single ? 1 : c->W, st);
+  }
   c->launches++;
   if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, std::string("gradient kernel launch: ") + cudaGetErrorString(e));
   return MCMC_B200_OK;
@@ -444,6 +504,7 @@ static AcceptParams base_accept_params(mcmc_b200_ctx* c) {
 static void fill_chain_accept(mcmc_b200_ctx* c, AcceptParams& a, int mode, int L) {
   a.mode = mode;
   a.slices = c->slices;
+  a.nslot = c->tab_nslot;
   const int last = (mode == ACC_BOOTSTRAP) ? 0 : (L - 1) & 1;
   a.partial = c->partial[last];
   a.ll_partial = c->llp[last];
@@ -486,16 +547,15 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   g.m_out = c->mbuf[(s + 1) & 1];
   g.g_carried = c->g_cur;
   g.partial_in = c->partial[(s + 1) & 1];
-  g.slices_in = c->slices;
   g.red_in = (c->comm && mode == MODE_NEXT) ? c->red : nullptr;
   g.partial_out = c->partial[s & 1];
   g.ll_out = c->llp[s & 1];
   g.eps = c->eps;
-  int r = launch_grad(c, g, c->slices, c->W, st);
+  int r = launch_grad(c, g, false, st);
   if (r) return r;
   if (c->comm) {
-    cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->P, c->Pp, c->red,
-                                           c->W, st);
+    cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->tab_nslot, c->P,
+                                           c->Pp, c->red, c->W, st);
     c->launches++;
     if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
     r = allreduce(c, c->red, (size_t)c->W * (c->Pp + 4), st);
@@ -668,7 +728,6 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
     g.m_out = (last && m_last) ? m_last : c->xm[(s + 1) & 1];
     g.g_carried = g0;
     g.partial_in = c->xpartial[(s + 1) & 1];
-    g.slices_in = S;
     g.red_in = (c->comm && g.mode == MODE_NEXT) ? c->xred : nullptr;
     g.partial_out = c->xpartial[s & 1];
     g.ll_out = c->xllp[s & 1];
@@ -676,10 +735,11 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
     g.eps_scalar = eps;
     g.row_loss = last ? row_loss : nullptr;
     g.row_loss_stride = 0;
-    int r = launch_grad(c, g, S, 1, st, (eval_only && c->cfg.precision == MCMC_B200_PREC_TF32) ? c->dbg : nullptr);
+    int r = launch_grad(c, g, true, st, (eval_only && c->cfg.precision == MCMC_B200_PREC_TF32) ? c->dbg : nullptr);
     if (r) return r;
     if (c->comm) {
-      cudaError_t e = launch_reduce_partials(c->xpartial[s & 1], c->xllp[s & 1], S, c->P, c->Pp, c->xred, 1, st);
+      cudaError_t e = launch_reduce_partials(c->xpartial[s & 1], c->xllp[s & 1], S, c->xtab_nslot, c->P, c->Pp,
+                                             c->xred, 1, st);
       c->launches++;
       if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
       r = allreduce(c, c->xred, (size_t)(c->Pp + 4), st);
@@ -689,6 +749,7 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
   AcceptParams a = base_accept_params(c);
   a.mode = ACC_FINALIZE;
   a.slices = S;
+  a.nslot = c->xtab_nslot;
   a.partial = c->xpartial[(L - 1) & 1];
   a.ll_partial = c->xllp[(L - 1) & 1];
   a.red_in = c->comm ? c->xred : nullptr;

@@ -32,12 +32,13 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
   const uint32_t gwin = a.gwin ? (uint32_t)a.gwin[win] : 0u;
 
   // log-likelihood of the proposal: fixed-order sum of the slice partials
+  const int ns = a.nslot ? a.nslot[win] : a.slices;
   double ll_new;
   if (a.red_in) {
     ll_new = a.red_in[(size_t)win * (a.Pp + 4) + a.Pp];
   } else {
     ll_new = 0.0;
-    for (int s = 0; s < a.slices; ++s) ll_new += a.ll_partial[(size_t)win * a.slices + s];
+    for (int s = 0; s < ns; ++s) ll_new += a.ll_partial[(size_t)win * a.slices + s];
   }
 
   constexpr int MAXPT = 16;  // parameters per thread (P <= 4096)
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
     } else {
       const float* pi = a.partial + (size_t)win * a.slices * a.Pp + p;
       g = 0.f;
-      for (int s = 0; s < a.slices; ++s) g += pi[(size_t)s * a.Pp];
+      for (int s = 0; s < ns; ++s) g += pi[(size_t)s * a.Pp];
     }
     g = fmaf(w, a.prior.neg_inv_s2, g);
     const float q = w * a.prior.inv_s;
@@ -172,29 +173,32 @@ cudaError_t launch_repack(const float* x, const float* y, float* out, long long 
 
 // ---- row sharding: this rank's sums, as doubles, ready for the allreduce ---
 __global__ void reduce_partials_kernel(const float* __restrict__ partial,
-                                       const double* __restrict__ ll_partial, int slices, int P,
-                                       int Pp, double* __restrict__ red) {
+                                       const double* __restrict__ ll_partial, int slices,
+                                       const int* __restrict__ nslot, int P, int Pp,
+                                       double* __restrict__ red) {
   const int win = blockIdx.y;
+  const int ns = nslot ? nslot[win] : slices;
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
   double* r = red + (size_t)win * (Pp + 4);
   if (p < P) {
     const float* pi = partial + (size_t)win * slices * Pp + p;
     float g = 0.f;
-    for (int s = 0; s < slices; ++s) g += pi[(size_t)s * Pp];
+    for (int s = 0; s < ns; ++s) g += pi[(size_t)s * Pp];
     r[p] = (double)g;
   } else if (p == Pp) {
     double s = 0.0;
-    for (int i = 0; i < slices; ++i) s += ll_partial[(size_t)win * slices + i];
+    for (int i = 0; i < ns; ++i) s += ll_partial[(size_t)win * slices + i];
     r[Pp] = s;
   } else if (p < Pp + 4) {
     r[p] = 0.0;
   }
 }
 
-cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices, int P,
-                                   int Pp, double* red, int windows, cudaStream_t st) {
+cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices,
+                                   const int* nslot, int P, int Pp, double* red, int windows,
+                                   cudaStream_t st) {
   dim3 grid((Pp + 4 + 255) / 256, windows);
-  reduce_partials_kernel<<<grid, 256, 0, st>>>(partial, ll_partial, slices, P, Pp, red);
+  reduce_partials_kernel<<<grid, 256, 0, st>>>(partial, ll_partial, slices, nslot, P, Pp, red);
   return cudaGetLastError();
 }
 

@@ -14,7 +14,8 @@ enum AcceptMode : int {
 struct AcceptParams {
   int mode;
   int P, Pp;
-  int slices;
+  int slices;                // slots per window (stride, and count when nslot is null)
+  const int* nslot;          // optional [windows]: slots in use
   const float* partial;      // [windows][slices][Pp] of the last gradient launch
   const double* ll_partial;  // [windows][slices]
   const double* red_in;      // row sharding: [windows][Pp + 4] all-reduced sums, else null
@@ -54,8 +55,9 @@ struct AcceptParams {
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st);
 cudaError_t launch_repack(const float* x, const float* y, float* out, long long n_rows,
                           long long rows_pad, int D, cudaStream_t st);
-cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices, int P,
-                                   int Pp, double* red, int windows, cudaStream_t st);
+cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices,
+                                   const int* nslot, int P, int Pp, double* red, int windows,
+                                   cudaStream_t st);
 cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
                            float* out, cudaStream_t st);
 cudaError_t launch_log_acpt(const float* prev_loss, const float* new_loss, long long n_loss,
@@ -67,11 +69,10 @@ cudaError_t launch_grad_fp32(int H, const GradParams& g, int slices, int windows
 int fp32_max_ctas_per_sm(int H);
 int fp32_tile_rows(int H);
 
-// TF32 (tcgen05) path; `tmap` / `tmap_mn` are CUtensorMaps over the repacked dataset that stage a
-// row tile with 16-byte-chunk and with 32-byte-chunk swizzling
-cudaError_t launch_grad_tf32(int H, const void* tmap, const void* tmap_mn, const GradParams& g, int slices,
-                             int windows, float* dbg, cudaStream_t st);
-int tf32_max_ctas_per_sm(int H);
+// TF32 (tcgen05) path: persistent, one CTA per SM; `tmap_mn` is a CUtensorMap over the repacked
+// dataset that stages a row tile with the 32-byte-chunk swizzle
+cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
+                             cudaStream_t st);
 int tf32_supported(int H);
 constexpr int TF32_TILE = 128;
 

@@ -52,7 +52,12 @@ struct GradParams {
   float* m_out;
   const float* g_carried;   // MODE_FIRST
   const float* partial_in;  // MODE_NEXT: [windows][slices_in][Pp] likelihood-gradient partials
-  int slices_in;
+  int slices_in;            // slots per window in partial_in (stride, and count when nslot_in is null)
+  const int* nslot_in;      // optional [windows]: slots of partial_in that are in use
+  // persistent (one CTA per SM) kernels: which tile ranges this launch's CTAs own
+  const int* seg_ptr;       // [ctas + 1] first segment of each CTA
+  const int4* segs;         // {window, first tile, end tile, slot}
+  int slices_out;           // slots per window in partial_out / ll_out
   const double* red_in;     // MODE_NEXT with row sharding: [windows][Pp + 4] all-reduced sums
   float* partial_out;       // [windows][slices][Pp]
   double* ll_out;           // [windows][slices]
@@ -119,8 +124,9 @@ __device__ __forceinline__ float leapfrog_param(const GradParams& g, int win, in
       grad = (float)g.red_in[(size_t)win * (g.Pp + 4) + p];
     } else {
       const float* pi = g.partial_in + (size_t)win * g.slices_in * g.Pp + p;
+      const int ns = g.nslot_in ? g.nslot_in[win] : g.slices_in;
       grad = 0.f;
-      for (int s = 0; s < g.slices_in; ++s) grad += pi[(size_t)s * g.Pp];
+      for (int s = 0; s < ns; ++s) grad += pi[(size_t)s * g.Pp];
     }
     grad = fmaf(w, g.prior.neg_inv_s2, grad);  // prior gradient at the previous point
     kick = 1.f;
@@ -147,6 +153,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
                : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   uint32_t ok;
