@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the HMC hot path.
+
+Workload (BASELINE.json configs[2]): 200 independent windows, each 58368 x 22
+FP32 rows of synthetic data (X ~ N(0,1), y = teacher MLP + noise, from the
+seeded generator in the library), one 22 -> 40 -> 1 chain per window, Gaussian
+sigma = 1 likelihood, N(0,1) prior, L = 10 leapfrog steps, eps = 1e-3, TF32
+tensor-core mode.  Windows are sharded 200/N over N GPUs with no communication.
+
+A "step" is one HMC iteration of every window: L = 10 full-batch gradient
+evaluations per window plus the accept kernel.  `value` is kept samples per
+second over all windows and GPUs with the data resident in HBM; `e2e` is the
+same metric through the C-ABI from pinned HOST buffers (dataset upload, the
+chain, sample download all inside the timed region).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W]
+  python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...
+  python bench.py --impl reference      # the CPU port of the reference's math
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WINDOWS = 200
+ROWS = 58368
+D, H, P = 22, 40, 961
+LEAPFROG = 10
+EPS = 1e-3
+SEED = 2024
+ALG_BYTES_PER_ROW = 92          # 22 features + y, FP32: what one gradient must read per row
+METRIC = "hmc_samples_per_sec_all_windows"
+UNIT = "samples/s"
+# DRAM traffic of the gradient kernel per row, from the ncu capture summarised in
+# profiles/grad_tf32_kernel_w32.md (dram read + write bytes of one launch / rows of that launch)
+NCU_DRAM_BYTES_PER_ROW = 97.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device):
+        self.device = device
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.device), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"),
+                               f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": float(max(mx)) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_port_rate(seconds_budget, nthreads=0, max_iters=4096):
+    """Samples/s of the FP32 CPU port (oracle/) on ONE window of the same workload."""
+    import mcmc_bnn_example_b200 as m
+    import oracle as O
+    x, y, _ = m.synth_window(SEED, 0, ROWS)
+    model, sampler = O.baseline_model(), O.baseline_sampler(L=LEAPFROG, eps=EPS)
+    rng = np.random.default_rng(0)
+    threads = O.max_threads() if nthreads <= 0 else nthreads
+    # one warm-up iteration, then as many as fit the budget
+    mom = rng.standard_normal((1, P)).astype(np.float32)
+    lu = np.log(rng.uniform(size=1)).astype(np.float32)
+    t0 = time.perf_counter()
+    O.port_f32_chain(model, sampler, x, y, mom, lu, nthreads=threads, want_samples=False)
+    one = time.perf_counter() - t0
+    n = int(max(2, min(max_iters, seconds_budget / max(one, 1e-3))))
+    mom = rng.standard_normal((n, P)).astype(np.float32)
+    lu = np.log(rng.uniform(size=n)).astype(np.float32)
+    t0 = time.perf_counter()
+    O.port_f32_chain(model, sampler, x, y, mom, lu, nthreads=threads, want_samples=False)
+    dt = time.perf_counter() - t0
+    # the port also evaluates the bootstrap gradient once per call: n*L + 1 gradients
+    return n / dt, threads, n, dt
+
+
+def run_reference(args):
+    """The reference has no CPU implementation of its model (all of its arithmetic is CUDA device
+    code), so this arm times the plain host FP32 transcription of its math in oracle/, on all host
+    cores, on a bounded sample of the same workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rates = []
+    iters = 0
+    for _ in range(max(1, args.warmup > 0)):
+        cpu_port_rate(2.0)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        r, threads, n, dt = cpu_port_rate(max(1.0, 60.0 / max(args.steps, 1)), max_iters=8)
+        rates.append(r)
+        iters += n
+    wall = time.perf_counter() - t0
+    value = float(np.mean(rates))
+    sample = ("each step = %d HMC iterations (L=%d) of 1 of the %d windows (%d rows); the full step is "
+              "%dx this" % (iters // max(args.steps, 1), LEAPFROG, WINDOWS, ROWS, WINDOWS))
+    out = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * wall / max(args.steps, 1),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "BASELINE configs[2]: 200 windows x 58368 rows x 22 features, 22-40-1 MLP, "
+                               "L=10, eps=1e-3; CPU arm runs a bounded sample of it",
+                   "windows": WINDOWS, "rows": ROWS, "leapfrog_steps": LEAPFROG},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--windows", type=int, default=WINDOWS, help="total windows over all GPUs")
+    ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import mcmc_bnn_example_b200 as m
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    else:
+        dist = None
+        torch.cuda.set_device(0)
+    dev = torch.device("cuda", local_rank)
+    n_gpus = world
+
+    # windows are independent: rank r takes the contiguous block of global windows [w0, w1)
+    w0 = rank * args.windows // world
+    w1 = (rank + 1) * args.windows // world
+    n_local = w1 - w0
+    prec = m.PREC_TF32 if args.precision == "tf32" else m.PREC_FP32
+    K, W = args.steps, args.warmup
+
+    # synthetic dataset in pinned host memory (also the source of the e2e uploads)
+    xh = torch.empty((n_local, ROWS, D), dtype=torch.float32, pin_memory=True)
+    yh = torch.empty((n_local, ROWS), dtype=torch.float32, pin_memory=True)
+    xn, yn = xh.numpy(), yh.numpy()
+    for i in range(n_local):
+        xi, yi, _ = m.synth_window(SEED, w0 + i, ROWS)
+        xn[i], yn[i] = xi, yi
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def make_ctx(sample_capacity):
+        cfg = m.baseline_config(precision=prec, seed=SEED, sample_capacity=sample_capacity,
+                                leapfrog_steps=LEAPFROG, eps0=EPS)
+        return m.Context(cfg, n_windows=n_local, rows=ROWS, device=local_rank)
+
+    def upload(ctx):
+        for i in range(n_local):
+            ctx.set_window_data_ptr(i, xh[i].data_ptr(), yh[i].data_ptr(), is_device=False,
+                                    global_window=w0 + i)
+
+    # ---------------- device-resident measurement ----------------
+    ctx = make_ctx(0)
+    upload(ctx)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    ctx.run_chain(W)  # bootstrap + warm-up iterations (graph capture happens here)
+    ctx.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(local_rank)
+    barrier()
+    torch.cuda.synchronize()
+    sampler.start()
+    e0.record(stream)
+    ctx.run_chain(K, sync=False)
+    e1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    barrier()
+    clocks = sampler.stop()
+    ms = e0.elapsed_time(e1)
+    launches = ctx.launch_count()
+    geom = ctx.geometry()
+    acc = [ctx.chain_info(i)["accepted"] for i in range(min(n_local, 4))]
+    ctx.close()
+    del ctx
+
+    # ---------------- end-to-end through the C-ABI with host buffers ----------------
+    e2e_ms = None
+    h2d = d2h = 0
+    if not args.no_e2e:
+        sh = torch.empty((n_local, K, P), dtype=torch.float32, pin_memory=True)
+        warm = make_ctx(K)  # warm-up of the same call sequence (allocations, graph instantiation)
+        upload(warm)
+        warm.run_chain(min(K, 3))
+        warm.close()
+        barrier()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        c2 = make_ctx(K)
+        upload(c2)                                  # H2D of X and y from pinned memory
+        c2.run_chain(K)                             # bootstrap + K iterations
+        for i in range(n_local):                    # D2H of the K samples of every window
+            c2.get_samples_ptr(i, 0, K, sh[i].data_ptr())
+        torch.cuda.synchronize()
+        e2e_ms = 1e3 * (time.perf_counter() - t0)
+        c2.close()
+        h2d = n_local * ROWS * (D + 1) * 4
+        d2h = n_local * K * P * 4
+        barrier()
+
+    # ---------------- reduce over ranks: max time, summed bytes/launches ----------------
+    if dist is not None:
+        t = torch.tensor([ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_max = float(t[0]), float(t[1])
+        s = torch.tensor([float(launches), float(h2d), float(d2h)], device=dev, dtype=torch.float64)
+        dist.all_reduce(s, op=dist.ReduceOp.SUM)
+        launches, h2d, d2h = int(s[0]), int(s[1]), int(s[2])
+        if e2e_ms is not None:
+            e2e_ms = e2e_max
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    value = args.windows * K / (ms * 1e-3)
+    peak, peak_src = measured_peaks()
+    # dominant kernel = the fused gradient kernel; L launches per step per GPU.  Its average launch
+    # duration is bounded above by (timed region) / (K * L): the accept kernel's few microseconds
+    # per step and any launch gaps are charged to it.
+    grad_ms = ms / (K * LEAPFROG)
+    rows_per_launch = n_local * ROWS  # per GPU (rank 0's share; shares differ by at most one window)
+    achieved = ALG_BYTES_PER_ROW * rows_per_launch / (grad_ms * 1e-3) / 1e9
+    out = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": K, "warmup": W,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": args.precision, "data": "synthetic",
+        "config": {
+            "workload": "BASELINE configs[2]: 200 windows x 58368 rows x 22 features FP32, 22-40-1 MLP "
+                        "(961 params), Gaussian sigma=1, N(0,1) prior, L=10, eps=1e-3, windows sharded "
+                        "200/N with no communication",
+            "windows": args.windows, "windows_per_gpu": n_local, "rows": ROWS, "leapfrog_steps": LEAPFROG,
+            "gradients_per_sec": value * LEAPFROG,
+            "l2": "inputs larger than L2 between timed iterations (%.0f MB per GPU vs 126 MB L2)"
+                  % (n_local * ROWS * 96 / 1e6),
+            "geometry": geom, "accepted_first_windows": acc,
+        },
+        "clocks": clocks,
+        "gpu_launches": launches,
+        "roofline": {
+            "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "peak_source": peak_src,
+            "kernel": "grad_tf32_kernel" if args.precision == "tf32" else "grad_fp32_kernel",
+            "algorithmic_bytes_per_launch": ALG_BYTES_PER_ROW * rows_per_launch,
+            "avg_launch_ms": grad_ms,
+            "traffic": NCU_DRAM_BYTES_PER_ROW * rows_per_launch,
+        },
+    }
+    if e2e_ms is not None:
+        out["e2e"] = {"value": args.windows * K / (e2e_ms * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,
+                      "note": "one run_chain call per measurement: dataset upload from pinned host "
+                              "memory once, K iterations, K samples per window read back; bytes are "
+                              "totals over GPUs divided by K"}
+    if not args.no_cpu:
+        r, threads, n, dt = cpu_port_rate(12.0)
+        out["cpu_baseline"] = {
+            "value": r, "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": "%d HMC iterations (L=%d, %d gradients) of 1 of the %d windows in %.1f s; the "
+                      "reference has no CPU code, this is the FP32 host port of its math in oracle/"
+                      % (n, LEAPFROG, n * LEAPFROG + 1, WINDOWS, dt)}
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

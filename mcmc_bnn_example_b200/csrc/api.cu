@@ -8,6 +8,7 @@
 #include <dlfcn.h>
 #include <math.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -461,6 +462,7 @@ static GradParams base_grad_params(mcmc_b200_ctx* c) {
   g.lik = make_lik(c->cfg);
   g.prior = make_prior(c->cfg);
   g.status = c->status;
+  { const char* a = getenv("MCMC_B200_ABLATE"); g.ablate = a ? atoi(a) : 0; }
   return g;
 }
 

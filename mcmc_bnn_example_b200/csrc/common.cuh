@@ -69,6 +69,7 @@ struct GradParams {
   LikParams lik;
   PriorParams prior;
   int* status;              // device error word (bounded waits that ran out)
+  int ablate;               // experiments only: bit mask of pipeline parts to skip (0 in production)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -168,13 +169,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after ~2^22 polls (well over a second), records the
-// code in the status word and returns false; the kernel then finishes with
-// whatever it has, so a lost copy can never hang the GPU.
+// try_wait that lets the hardware suspend the thread for up to `hint_ns` until the phase completes
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: the thread sleeps in hardware on the barrier in slices of 20 us and gives up after
+// 2^16 slices (about 1.3 s), records the code in the status word and returns false; the kernel then
+// finishes with whatever it has, so a lost copy or MMA can never hang the GPU.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
-  for (uint32_t i = 0; i < (1u << 22); ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (i > 64) __nanosleep(32);
+  if (mbar_try_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < (1u << 16); ++i) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   }
   if (status) atomicExch(status, code);
   return false;

@@ -295,6 +295,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           ok = ok && mbar_wait(&bar_e[wg], n & 1, g.status, 212);
           tc_fence_after();
           const uint32_t xa = smem_u32(xb + (wg * NST + n % NST) * G::TILE_BYTES);
+          if (!(g.ablate & 1))
 #pragma unroll
           for (int kb = 0; kb < TF32_TILE / 8; ++kb)
             tc_mma_tf32_ss(g_t, umma_desc_k128(ea + (kb >> 2) * G::ES_ATOM_BYTES + (kb & 3) * 32),
@@ -338,14 +339,20 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         }
 #pragma unroll
         for (int j = 0; j < 3; ++j) tc_st8(a_t + j * 8, xr[2 * j], xr[2 * j + 1]);
+        return xr[5].w;
+      };
+      // ... and tells the control thread once the stores have landed
+      auto publish_row = [&]() {
         tc_wait_st();
         tc_fence_before();
         mbar_arrive(&bar_a[wg]);
-        return xr[5].w;
       };
 
       float y = 0.f;
-      if (my_nt > 0) y = stage_row(n_done);
+      if (my_nt > 0) {
+        y = stage_row(n_done);
+        publish_row();
+      }
       for (int i = 0; i < my_nt; ++i) {
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
@@ -364,6 +371,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           dbg[wtid * 64 + 63] = y;
         }
         float pred = b1;
+        if (!(g.ablate & 8))
 #pragma unroll
         for (int j = 0; j < H; j += 4) {
           const float4 w1v = *reinterpret_cast<const float4*>(w1s + j);
@@ -376,6 +384,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           pred = fmaf(w1v.z, z[j + 2], pred);
           pred = fmaf(w1v.w, z[j + 3], pred);
         }
+        if (i + 1 < my_nt) publish_row();  // the tensor-memory stores have had the tanh pass to land
         const int grow = t * TF32_TILE + wtid;
         const bool valid = grow < g.n_rows;
         float loss, dy;
@@ -384,6 +393,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         llacc += (double)loss;
         if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
         db1 += dy;
+        if (!(g.ablate & 16))
 #pragma unroll
         for (int j = 0; j < H; ++j) {
           const float h = z[j];
@@ -399,6 +409,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           tma_load_2d(xb + (wg * NST + nn % NST) * G::TILE_BYTES, &tmap_mn, 0,
                       grow0 + (t0 + wg + (i - 1 + NST) * NWG) * TF32_TILE, &bar_tma[wg][nn % NST]);
         }
+ if (!(g.ablate & 4))
 #pragma unroll
         for (int j = 0; j < H; ++j)
           asm volatile("st.shared.f32 [%0], %1;" ::"r"(e_ptr[j & 7] + (uint32_t)(j * 128)), "f"(z[j]) : "memory");
