@@ -210,6 +210,30 @@ int mcmc_b200_log_acpt(mcmc_b200_ctx* ctx, const float* prev_loss, const float* 
                        const float* grad_cur, float eps, void* stream, float* out);
 
 /*
+ * log p and its gradient at w without any device allocation.  Has no
+ * counterpart in the reference (which allocates freely, main.h:156-183).
+ *
+ * For hosts that must not enter the CUDA allocator while they evaluate the
+ * model: an application that has given all GPU memory to its own arena, or a
+ * latency-critical loop where cudaMalloc/cudaFree would synchronise the device
+ * and stall every stream.  No context is needed: the scratch (repacked dataset,
+ * per-CTA gradient partials) is a fixed ~7.7 MB array inside the library image,
+ * held by every GPU that loads the library until the process exits.
+ *   limits : rows <= 65536, D = 22, H = 40, cfg->precision = FP32 (others are refused)
+ *   x [rows][22], y [rows], w [P] : DEVICE pointers (inputs)
+ *   grad [P], loglik_logprior [2] : DEVICE pointers (outputs: gradient; sum of
+ *                                   log-likelihoods, sum of log-priors)
+ * Runs on the current device, queued on `stream`; returns without waiting.
+ * The first call on a device looks up the array's address (once per device);
+ * make that call before any stream capture.  All calls on a GPU share the one
+ * array, which keeps the last call's contents: calls that overlap on the GPU
+ * (other streams, other threads) race — serialise them.
+ */
+int mcmc_b200_potential_and_grad_static(const mcmc_b200_config* cfg, const float* x, const float* y,
+                                        int64_t rows, const float* w, float* grad,
+                                        double* loglik_logprior, void* stream);
+
+/*
  * Synthetic window generator (host code, no GPU): X ~ N(0,1), teacher weights
  * ~ N(0, 0.3^2), y = teacher(X) + N(0, 0.05^2), all from Philox streams keyed
  * by (seed, window).  Stands in for the reference's missing data file

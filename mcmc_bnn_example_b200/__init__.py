@@ -21,7 +21,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libmcmc_b200.so")
-_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "synth.cu"]
+_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "synth.cu", "noalloc.cu"]
 _HEADERS = ["common.cuh", "chain.cuh", "philox.h"]
 
 OK = 0
@@ -37,7 +37,7 @@ EXPORTS = [
     "mcmc_b200_get_trace", "mcmc_b200_predict_mean", "mcmc_b200_final_loss",
     "mcmc_b200_nccl_unique_id", "mcmc_b200_enable_row_sharding", "mcmc_b200_mcmc_step",
     "mcmc_b200_log_acpt", "mcmc_b200_synth_window", "mcmc_b200_philox_normal", "mcmc_b200_philox_raw",
-    "mcmc_b200_launch_count", "mcmc_b200_chain_geometry",
+    "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
 ]
 
 
@@ -147,6 +147,13 @@ def philox_raw(ctr, key):
     o = (C.c_uint32 * 4)()
     lib().mcmc_b200_philox_raw(c, k, o)
     return list(o)
+
+
+def potential_and_grad_static(cfg, x_ptr, y_ptr, rows, w_ptr, grad_ptr, scalars_ptr, stream=None):
+    """Allocation-free log p / gradient on device pointers (see include/mcmc_b200.h); asynchronous."""
+    _check(lib().mcmc_b200_potential_and_grad_static(C.byref(cfg), _vp(x_ptr), _vp(y_ptr), C.c_int64(rows),
+                                                     _vp(w_ptr), _vp(grad_ptr), _vp(scalars_ptr),
+                                                     _vp(stream)))
 
 
 def nccl_unique_id():

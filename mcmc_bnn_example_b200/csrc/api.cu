@@ -30,6 +30,8 @@ static int fail(int code, const std::string& msg) {
   g_last_error = msg;
   return code;
 }
+// for the other translation units of the library
+void mcmc_b200_set_last_error(const std::string& msg) { g_last_error = msg; }
 
 #define CK(call)                                                                              \
   do {                                                                                        \
