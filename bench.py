@@ -196,8 +196,8 @@ def main():
     n_gpus = world
 
     # windows are independent: rank r takes the contiguous block of global windows [w0, w1)
-    w0 = rank * args.windows // world
-    w1 = (rank + 1) * args.windows // world
+    from mcmc_bnn_example_b200.sharding import window_block
+    w0, w1 = window_block(rank, world, args.windows)
     n_local = w1 - w0
     prec = m.PREC_TF32 if args.precision == "tf32" else m.PREC_FP32
     K, W = args.steps, args.warmup

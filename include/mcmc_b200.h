@@ -61,7 +61,9 @@ typedef struct mcmc_b200_config {
   double increment;        /* STEP_SIZE_INCREMENT (0.01) */
   uint64_t seed;           /* SEED_INIT; keys the Philox streams */
   int32_t trace_iters;     /* first K iterations whose draws and energies are recorded */
-  int32_t slices;          /* CTAs per window per launch; 0 = chosen from the SM count */
+  int32_t slices;          /* pieces each window is cut into per launch; 0 = chosen from the SM count
+                              (fastest).  A fixed value makes a window's results bit-identical
+                              however many windows share the context or the GPU. */
 } mcmc_b200_config;
 
 /* Fills a config with the reference's shipped preset (global_params.h:27-58)

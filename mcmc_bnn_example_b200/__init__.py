@@ -70,6 +70,8 @@ def build(force=False, verbose=False):
            "-o", LIB_PATH] + src + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
+    if os.environ.get("MCMC_B200_EXPERIMENTS"):
+        cmd.insert(1, "-DMCMC_B200_EXPERIMENTS")  # ablation / phase-timing hooks in the TF32 kernel
     subprocess.check_call(cmd)
     return LIB_PATH
 

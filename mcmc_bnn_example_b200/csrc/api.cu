@@ -239,7 +239,8 @@ static int make_tensor_map(mcmc_b200_ctx* c) {
 // Cuts the flattened (window, tile) list of a launch into one contiguous range per CTA and each
 // range into per-window segments; slot = the segment's index among its window's segments.
 static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
-                            int** d_seg_ptr, int4** d_segs, int** d_nslot, int* n_ctas, int* max_slots);
+                            int chunks_per_window, int** d_seg_ptr, int4** d_segs, int** d_nslot,
+                            int* n_ctas, int* max_slots);
 
 API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows, int64_t rows,
                          mcmc_b200_ctx** out) {
@@ -281,13 +282,15 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   cudaError_t es = cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking);
   if (es != cudaSuccess) { delete c; return fail(MCMC_B200_ERR_CUDA, "cudaStreamCreate failed"); }
   if (tf32) {
-    // persistent kernel: cfg.slices, when given, is the number of CTAs of a launch
-    const int max_ctas = cfg->slices > 0 ? cfg->slices : c->num_sms;
-    int r_ = build_work_table(c, n_windows, n_tiles, max_ctas, &c->tab_seg_ptr, &c->tab_segs, &c->tab_nslot,
-                              &c->tab_ctas, &c->slices);
+    // persistent kernel: by default every CTA gets an equal share of the launch's tiles, so where a
+    // window is cut depends on how many windows share the launch.  cfg.slices > 0 instead cuts every
+    // window into that many fixed chunks (whole chunks per CTA): a window's result is then bit-identical
+    // wherever and with whatever else it runs, at some cost in load balance.
+    int r_ = build_work_table(c, n_windows, n_tiles, c->num_sms, cfg->slices, &c->tab_seg_ptr, &c->tab_segs,
+                              &c->tab_nslot, &c->tab_ctas, &c->slices);
     if (r_ == MCMC_B200_OK)
-      r_ = build_work_table(c, 1, n_tiles, max_ctas, &c->xtab_seg_ptr, &c->xtab_segs, &c->xtab_nslot,
-                            &c->xtab_ctas, &c->slices_x);
+      r_ = build_work_table(c, 1, n_tiles, c->num_sms, cfg->slices, &c->xtab_seg_ptr, &c->xtab_segs,
+                            &c->xtab_nslot, &c->xtab_ctas, &c->slices_x);
     if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
   } else {
     const long long capacity = (long long)c->num_sms * c->ctas_per_sm;
@@ -356,23 +359,40 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
 }
 
 static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
-                            int** d_seg_ptr, int4** d_segs, int** d_nslot, int* n_ctas, int* max_slots) {
+                            int chunks_per_window, int** d_seg_ptr, int4** d_segs, int** d_nslot,
+                            int* n_ctas, int* max_slots) {
   const long long T = (long long)windows * tiles_per_window;
-  long long G = max_ctas;
-  if (G > T) G = T;
-  if (G < 1) G = 1;
-  std::vector<int> seg_ptr(G + 1, 0), nslot(windows, 0);
+  std::vector<int> seg_ptr, nslot(windows, 0);
   std::vector<int4> segs;
-  for (long long b = 0; b < G; ++b) {
-    long long s = b * T / G;
-    const long long e = (b + 1) * T / G;
-    seg_ptr[b] = (int)segs.size();
-    while (s < e) {
-      const long long w = s / tiles_per_window;
-      const long long wend = std::min(e, (w + 1) * tiles_per_window);
-      segs.push_back(make_int4((int)w, (int)(s - w * tiles_per_window), (int)(wend - w * tiles_per_window),
-                               nslot[w]++));
-      s = wend;
+  long long G;
+  if (chunks_per_window > 0) {
+    long long cpw = std::min<long long>(std::min<long long>(chunks_per_window, tiles_per_window), MAX_SLICES);
+    const long long NC = (long long)windows * cpw;
+    G = std::min<long long>(max_ctas, NC);
+    seg_ptr.assign(G + 1, 0);
+    for (long long b = 0; b < G; ++b) {
+      seg_ptr[b] = (int)segs.size();
+      for (long long ch = b * NC / G; ch < (b + 1) * NC / G; ++ch) {
+        const long long w = ch / cpw, k = ch % cpw;
+        segs.push_back(make_int4((int)w, (int)(k * tiles_per_window / cpw), (int)((k + 1) * tiles_per_window / cpw),
+                                 (int)k));
+        nslot[w] = (int)cpw;
+      }
+    }
+  } else {
+    G = std::max<long long>(1, std::min<long long>(max_ctas, T));
+    seg_ptr.assign(G + 1, 0);
+    for (long long b = 0; b < G; ++b) {
+      long long s = b * T / G;
+      const long long e = (b + 1) * T / G;
+      seg_ptr[b] = (int)segs.size();
+      while (s < e) {
+        const long long w = s / tiles_per_window;
+        const long long wend = std::min(e, (w + 1) * tiles_per_window);
+        segs.push_back(make_int4((int)w, (int)(s - w * tiles_per_window), (int)(wend - w * tiles_per_window),
+                                 nslot[w]++));
+        s = wend;
+      }
     }
   }
   seg_ptr[G] = (int)segs.size();
@@ -555,7 +575,7 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   g.partial_out = c->partial[s & 1];
   g.ll_out = c->llp[s & 1];
   g.eps = c->eps;
-  int r = launch_grad(c, g, false, st);
+  int r = launch_grad(c, g, false, st, (g.ablate & 512) ? c->dbg : nullptr);
   if (r) return r;
   if (c->comm) {
     cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->tab_nslot, c->P,

@@ -70,9 +70,10 @@ struct Tf32Geom {
   static constexpr int P = D * H + 2 * H + 1;
   static constexpr size_t SMEM = 1024 + XB_BYTES + ES_BYTES + W0S_BYTES + W1_BYTES;
   // tensor-memory columns: A operand and forward accumulator per warpgroup, one backward accumulator
-  static constexpr int A_COL0 = 0, A_STRIDE = 32;
-  static constexpr int Z_COL0 = TF32_NWG * A_STRIDE, Z_STRIDE = 64;
-  static constexpr int G_COL0 = Z_COL0 + TF32_NWG * Z_STRIDE, G_STRIDE = 32;
+  // (the forward accumulator is double-buffered: forward(n+1) runs while Z(n) is being consumed)
+  static constexpr int A_COL0 = 0, A_STRIDE = 24;
+  static constexpr int Z_COL0 = TF32_NWG * A_STRIDE, Z_STRIDE = NF;
+  static constexpr int G_COL0 = Z_COL0 + 2 * TF32_NWG * Z_STRIDE, G_STRIDE = 24;
   static constexpr int TMEM_COLS = 512;
   static_assert(H % 8 == 0 && H <= 64, "hidden width must be a multiple of 8, at most 64");
   static_assert(G_COL0 + TF32_NWG * G_STRIDE <= TMEM_COLS, "tensor memory budget");
@@ -170,8 +171,43 @@ __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_ma
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
-// bounded poll used by the control thread while it serves several warpgroups
-constexpr uint32_t CTRL_POLL_LIMIT = 1u << 24;
+// Named hardware barriers hand work from a warpgroup (128 arriving threads) to its control warp
+// (32 waiting threads): a few tens of cycles, no polling.  Ids 1..NWG are the warpgroups' own barriers.
+constexpr int BAR_ROWS0 = 4;   // + wg: rows of a tile are in tensor memory
+constexpr int BAR_E0 = 8;      // + wg: E of a tile is in shared memory
+__device__ __forceinline__ void named_arrive(int id, int count) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_sync(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+// Experiments (built only with -DMCMC_B200_EXPERIMENTS): ABL(bit) skips a part of the pipeline when
+// that bit is set in GradParams::ablate, PROF_MARK accumulates clock64 deltas per phase in thread 0 of
+// each warpgroup of CTA 0.  In the production build both vanish at compile time.
+#ifdef MCMC_B200_EXPERIMENTS
+#define ABL(bit) ((g.ablate & (bit)) != 0)
+#define PROF_DECL                                                                        \
+  const bool prof = dbg && ABL(512) && blockIdx.x == 0 && wtid == 0;             \
+  long long pacc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};                                   \
+  long long plast = clock64();
+#define PROF_MARK(k)                                   \
+  if (prof) {                                          \
+    const long long now_ = clock64();                  \
+    pacc[k] += now_ - plast;                           \
+    plast = now_;                                      \
+  }
+#define PROF_FLUSH                                                                        \
+  if (prof) {                                                                             \
+    for (int k = 0; k < 10; ++k) dbg[12288 + wg * 16 + k] += (float)pacc[k];              \
+    dbg[12288 + wg * 16 + 10] += (float)my_nt;                                            \
+  }
+#else
+#define ABL(bit) false
+#define PROF_DECL
+#define PROF_MARK(k)
+#define PROF_FLUSH
+#endif
 
 template <int H>
 __global__ void __launch_bounds__(TF32_THREADS, 1)
@@ -247,7 +283,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
 
     // ---- segment prologue: start the first row tiles, fused leapfrog update, stage W0a ----
     const int my_nt = is_ctrl ? 0 : (nt - wg + NWG - 1) / NWG;  // tiles t0 + wg, t0 + wg + NWG, ...
-    if (!is_ctrl && wtid == 0) {
+    if (!is_ctrl && wtid == 0 && !ABL(256)) {
       for (int i = 0; i < NST && i < my_nt; ++i) {
         const uint32_t n = n_done + i;
         mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
@@ -271,41 +307,57 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     __syncthreads();
 
     if (is_ctrl) {
-      // ---- control thread of warpgroup `wg`.  The warpgroup hands over the rows of tile n+1
-      //      (forward A operand in tensor memory) before it hands over E of tile n, so the
-      //      forward MMAs of the next tile run while the warpgroup is busy with the current one. ----
-      if (lane == 0) {
-        const int cnt = (nt - wg + NWG - 1) / NWG;
-        const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
-        const uint32_t z_t = tmem + G::Z_COL0 + wg * G::Z_STRIDE;
-        const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
-        const uint32_t ea = smem_u32(es + wg * G::ES_WG_BYTES);
-        auto issue_fwd = [&](uint32_t n) {
-          ok = ok && mbar_wait(&bar_a[wg], n & 1, g.status, 211);
+      // ---- control warp of warpgroup `wg`: waits on the warpgroup's hardware barriers with all 32
+      //      lanes, lane 0 issues.  Order per tile n: forward(n+1) as soon as its rows are in tensor
+      //      memory (the warpgroup stages them at the START of tile n), backward(n) when E(n) is in
+      //      shared memory; forward accumulators alternate between two buffers. ----
+      const int cnt = (nt - wg + NWG - 1) / NWG;
+      const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
+      const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE;
+      const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
+      const uint32_t ea = smem_u32(es + wg * G::ES_WG_BYTES);
+      auto issue_fwd = [&](uint32_t n) {
+        named_sync(BAR_ROWS0 + wg, 160);
+        if (lane == 0) {
           tc_fence_after();
+          const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
+          if (!ABL(32))
 #pragma unroll
           for (int kb = 0; kb < 3; ++kb)
             tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_k128(w0s_addr + kb * 32), IDESC_FWD, kb > 0);
           tc_commit(&bar_fwd[wg]);
-        };
-        if (cnt > 0) issue_fwd(c_issued);
-        for (int i = 0; i < cnt && ok; ++i) {
-          const uint32_t n = c_issued + i;
-          if (i + 1 < cnt) issue_fwd(n + 1);
-          ok = ok && mbar_wait(&bar_e[wg], n & 1, g.status, 212);
+        }
+        __syncwarp();
+      };
+      if (cnt > 0) issue_fwd(c_issued);
+      for (int i = 0; i < cnt; ++i) {
+        const uint32_t n = c_issued + i;
+        if (i + 1 < cnt) issue_fwd(n + 1);
+        named_sync(BAR_E0 + wg, 160);
+        if (lane == 0) {
           tc_fence_after();
           const uint32_t xa = smem_u32(xb + (wg * NST + n % NST) * G::TILE_BYTES);
-          if (!(g.ablate & 1))
+          if (!ABL(1))
 #pragma unroll
           for (int kb = 0; kb < TF32_TILE / 8; ++kb)
             tc_mma_tf32_ss(g_t, umma_desc_k128(ea + (kb >> 2) * G::ES_ATOM_BYTES + (kb & 3) * 32),
                            umma_desc_mn32(xa + kb * 1024, G::TILE_BYTES), IDESC_BWD,
                            (i == 0 && kb == 0) ? 0u : 1u);
           tc_commit(&bar_bwd[wg]);
+          // this tile's row stage is free as soon as those MMAs have completed: refill it with the
+          // tile NST ahead right then (a full tile of lead for the copy)
+          if (i + NST < cnt && !ABL(256) && !ABL(1024)) {
+            ok = ok && mbar_wait(&bar_bwd[wg], n & 1, g.status, 213);
+            if (ok) {
+              mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
+              tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
+                          grow0 + (t0 + wg + (i + NST) * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+            }
+          }
         }
-        c_issued += cnt;
+        __syncwarp();
       }
-      __syncwarp();
+      c_issued += cnt;
     } else {
       // ---- compute warpgroup: one row per thread ----
       float dw1[H];
@@ -316,7 +368,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       const float b1 = b1s;
       const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
       const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
-      const uint32_t z_t = tmem + G::Z_COL0 + wg * G::Z_STRIDE + lane_off;
+      const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE + lane_off;
       // E element (hidden j, row r): atom r/32 (= this warp), line j, 16-byte chunk (r%32)/4 ^ (j%8)
       uint32_t e_ptr[8];
 #pragma unroll
@@ -327,7 +379,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       // hands this thread's row of the landed tile to the tensor core (forward A operand); returns y
       auto stage_row = [&](uint32_t n) -> float {
         const int stage = n % NST;
-        ok = ok && mbar_wait(&bar_tma[wg][stage], (n / NST) & 1, g.status, 201);
+        if (!ABL(256)) ok = ok && mbar_wait(&bar_tma[wg][stage], (n / NST) & 1, g.status, 201);
         // 32-byte chunk j of a row sits at position j ^ (row % 4)
         const unsigned char* xrow = xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128;
         float4 xr[6];
@@ -337,6 +389,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           xr[2 * j] = *reinterpret_cast<const float4*>(cp);
           xr[2 * j + 1] = *reinterpret_cast<const float4*>(cp + 16);
         }
+        if (!ABL(64))
 #pragma unroll
         for (int j = 0; j < 3; ++j) tc_st8(a_t + j * 8, xr[2 * j], xr[2 * j + 1]);
         return xr[5].w;
@@ -345,33 +398,47 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       auto publish_row = [&]() {
         tc_wait_st();
         tc_fence_before();
-        mbar_arrive(&bar_a[wg]);
+        named_arrive(BAR_ROWS0 + wg, 160);
       };
 
+      PROF_DECL
       float y = 0.f;
       if (my_nt > 0) {
         y = stage_row(n_done);
         publish_row();
       }
+      PROF_MARK(9)
       for (int i = 0; i < my_nt; ++i) {
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
         ok = ok && mbar_wait(&bar_fwd[wg], n & 1, g.status, 202);
         tc_fence_after();
+        PROF_MARK(0)
+        // forward(n) is done with the A operand: the next tile's rows go in now, so that forward(n+1)
+        // (into the other accumulator buffer) has this whole tile's epilogue to complete
+        float y_next = 0.f;
+        if (i + 1 < my_nt) y_next = stage_row(n + 1);
+        PROF_MARK(1)
+        const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
         float z[H];
+        if (!ABL(128)) {
 #pragma unroll
         for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
         tc_wait_ld();
-        // Z is in registers: the next tile's rows can go to the tensor core right away
-        float y_next = 0.f;
-        if (i + 1 < my_nt) y_next = stage_row(n + 1);
-        if (dbg && blockIdx.x == 0 && sg == seg0 && wg == 0 && i == 0) {
+        } else {
+#pragma unroll
+        for (int c = 0; c < H; ++c) z[c] = 0.01f * c;
+        }
+        PROF_MARK(2)
+        if (i + 1 < my_nt) publish_row();
+        PROF_MARK(3)
+        if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0 && wg == 0 && i == 0) {
 #pragma unroll
           for (int j = 0; j < H; ++j) dbg[wtid * 64 + j] = z[j];
           dbg[wtid * 64 + 63] = y;
         }
         float pred = b1;
-        if (!(g.ablate & 8))
+        if (!ABL(8))
 #pragma unroll
         for (int j = 0; j < H; j += 4) {
           const float4 w1v = *reinterpret_cast<const float4*>(w1s + j);
@@ -384,7 +451,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           pred = fmaf(w1v.z, z[j + 2], pred);
           pred = fmaf(w1v.w, z[j + 3], pred);
         }
-        if (i + 1 < my_nt) publish_row();  // the tensor-memory stores have had the tanh pass to land
+        PROF_MARK(4)
         const int grow = t * TF32_TILE + wtid;
         const bool valid = grow < g.n_rows;
         float loss, dy;
@@ -393,30 +460,33 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         llacc += (double)loss;
         if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
         db1 += dy;
-        if (!(g.ablate & 16))
+        if (!ABL(16))
 #pragma unroll
         for (int j = 0; j < H; ++j) {
           const float h = z[j];
           dw1[j] = fmaf(dy, h, dw1[j]);
           z[j] = fmaf(-h, h, 1.f) * dy;  // E; the W1 factor is applied at read-out
         }
-        // the previous tile's backward MMAs are done with E and with their row tile:
-        // refill that stage with the tile NST ahead, then overwrite E
+        // the previous tile's backward MMAs must be done with E before it is overwritten
+        PROF_MARK(5)
         if (n > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n - 1) & 1, g.status, 203);
-        if (wtid == 0 && i >= 1 && i - 1 + NST < my_nt && ok) {
+        PROF_MARK(6)
+        if (wtid == 0 && i >= 1 && i - 1 + NST < my_nt && ok && ABL(1024)) {
           const uint32_t nn = n - 1 + NST;
           mbar_expect_tx(&bar_tma[wg][nn % NST], G::TILE_BYTES);
           tma_load_2d(xb + (wg * NST + nn % NST) * G::TILE_BYTES, &tmap_mn, 0,
                       grow0 + (t0 + wg + (i - 1 + NST) * NWG) * TF32_TILE, &bar_tma[wg][nn % NST]);
         }
- if (!(g.ablate & 4))
+ if (!ABL(4))
 #pragma unroll
         for (int j = 0; j < H; ++j)
           asm volatile("st.shared.f32 [%0], %1;" ::"r"(e_ptr[j & 7] + (uint32_t)(j * 128)), "f"(z[j]) : "memory");
         fence_proxy_async_smem();
-        mbar_arrive(&bar_e[wg]);
+        named_arrive(BAR_E0 + wg, 160);
         y = y_next;
+        PROF_MARK(7)
       }
+      PROF_FLUSH
       n_done += my_nt;
 
       // ---- this warpgroup's share of dW1 / db1 / log-lik (its row-tile stages are free now: scratch) ----
@@ -464,7 +534,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           for (int c = 0; c < NB; ++c) gacc[c] += g2[c];
         }
       }
-      if (dbg && blockIdx.x == 0 && sg == seg0) {
+      if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0) {
 #pragma unroll
         for (int c = 0; c < NB; ++c) dbg[8192 + tid * 32 + c] = gacc[c];
       }

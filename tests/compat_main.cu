@@ -33,7 +33,7 @@ int main(int argc, char** argv) {
   cudaMemcpyAsync(prev_mom.ptr(), hm.data(), NUM_PARAMS * 4, cudaMemcpyHostToDevice, stream);
   cudaMemcpyAsync(net.mom_next.ptr(), hm.data(), NUM_PARAMS * 4, cudaMemcpyHostToDevice, stream);
   net.do_swap();
-  const float eps = 0.2f;
+  const float eps = 0.02f;
   mcmc_step<float, 10>(data, labels, net.w_prev, net.w_next, net.mom_prev, net.mom_next, net.grad_prev,
                        net.grad_cur, net.grad_next, loss_values, nullptr, eps, stream);
   float* tmp_storage = nullptr;

@@ -48,11 +48,11 @@ def test_reference_style_program_matches_oracle(built):
     zero = np.zeros(P, np.float32)
     boot = O.logp_grad(model, x, y, zero, want_losses=True)
     mom = np.array([0.5 * ((i * 37) % 11 - 5) / 5.0 for i in range(P)], np.float32)
-    ref = O.mcmc_step(model, x, y, 10, 0.2, zero, mom, boot["grad"].astype(np.float32))
+    ref = O.mcmc_step(model, x, y, 10, 0.02, zero, mom, boot["grad"].astype(np.float32))
     assert np.abs(vals[:, 0] - ref["w_next"]).max() < 1e-5 * np.abs(ref["w_next"]).max()
     assert np.abs(vals[:, 1] - ref["grad_cur"]).max() < 1e-5 * np.abs(ref["grad_cur"]).max()
     prev = np.concatenate([boot["row_loss"], boot["prior_loss"]]).astype(np.float64)
-    mf = ref["mom_next"].astype(np.float64) + 0.5 * np.float32(0.2) * ref["grad_cur"].astype(np.float64)
+    mf = ref["mom_next"].astype(np.float64) + 0.5 * np.float32(0.02) * ref["grad_cur"].astype(np.float64)
     exp = float(np.sum(ref["loss_values"].astype(np.float64) - prev) +
                 0.5 * (np.sum(mom.astype(np.float64) ** 2) - np.sum(mf ** 2)))
     assert abs(la - exp) < 2e-2 + 1e-4 * abs(exp)

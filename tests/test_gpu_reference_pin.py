@@ -55,7 +55,7 @@ def test_oracle_and_cuda_path_against_reference_kernel(built):
     assert np.array_equal(r1["w_next"], w)
 
     # (2) ten leapfrog steps: mcmc_step<T,10>
-    eps = 0.2
+    eps = 0.02  # stable for 58368 rows: the trajectory does not amplify rounding differences
     g0 = o1["grad"].astype(np.float32)
     r10 = _ref_step(ref, x, y, 10, eps, w, mom, g0)
     o10 = O.mcmc_step(model, x, y, 10, eps, w, mom, g0)
