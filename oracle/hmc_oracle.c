@@ -7,7 +7,7 @@
  * path links, loads or calls it.  Only the test-suite, the smoke check and the
  * benchmark's CPU-baseline leg may use it.
  *
- * Parity pin: the reference ships no tests, golden vectors or CPU code, so the
+ * Parity PINNED: the reference ships no tests, golden vectors or CPU code, so the
  * oracle is pinned against outputs of the reference's own FP32 kernel
  * (`leapfrog_step_kernel`, built unmodified from its headers by
  * oracle/ref_harness.cu and run on a B200); the captured vectors live in
