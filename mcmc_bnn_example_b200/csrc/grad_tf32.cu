@@ -42,6 +42,7 @@
 #include <cuda.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <utility>
 #include "common.cuh"
 #include "chain.cuh"
 
@@ -169,6 +170,37 @@ __device__ __forceinline__ uint64_t umma_desc_mn32(uint32_t smem_addr, uint32_t 
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) |
          ((uint32_t)b_mn_major << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+// Packed FP32 pairs (sm_100 executes fma/mul on two floats per instruction)
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// E element stores with the line offset as an immediate (no address arithmetic per store)
+template <int J>
+__device__ __forceinline__ void store_e_one(const uint32_t* e_ptr, const float* z) {
+  asm volatile("st.shared.f32 [%0+%2], %1;" ::"r"(e_ptr[J & 7]), "f"(z[J]), "n"(J * 128) : "memory");
+}
+template <int... Js>
+__device__ __forceinline__ void store_e_all(const uint32_t* e_ptr, const float* z,
+                                            std::integer_sequence<int, Js...>) {
+  (store_e_one<Js>(e_ptr, z), ...);
 }
 
 // Named hardware barriers hand work from a warpgroup (128 arriving threads) to its control warp
@@ -360,9 +392,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       c_issued += cnt;
     } else {
       // ---- compute warpgroup: one row per thread ----
-      float dw1[H];
+      uint64_t dw1p[H / 2];  // dW1 accumulators, two hidden units per register pair
 #pragma unroll
-      for (int j = 0; j < H; ++j) dw1[j] = 0.f;
+      for (int j = 0; j < H / 2; ++j) dw1p[j] = 0ull;
       float db1 = 0.f;
       double llacc = 0.0;
       const float b1 = b1s;
@@ -460,12 +492,16 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         llacc += (double)loss;
         if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
         db1 += dy;
-        if (!ABL(16))
+        if (!ABL(16)) {
+          const uint64_t dy2 = pack2(dy, dy), one2 = pack2(1.f, 1.f);
 #pragma unroll
-        for (int j = 0; j < H; ++j) {
-          const float h = z[j];
-          dw1[j] = fmaf(dy, h, dw1[j]);
-          z[j] = fmaf(-h, h, 1.f) * dy;  // E; the W1 factor is applied at read-out
+          for (int j = 0; j < H; j += 2) {
+            const uint64_t h2 = pack2(z[j], z[j + 1]);
+            const uint64_t nh2 = pack2(-z[j], -z[j + 1]);
+            dw1p[j >> 1] = fma2(dy2, h2, dw1p[j >> 1]);
+            const uint64_t e2 = mul2(fma2(nh2, h2, one2), dy2);  // E; the W1 factor is applied at read-out
+            unpack2(e2, z[j], z[j + 1]);
+          }
         }
         // the previous tile's backward MMAs must be done with E before it is overwritten
         PROF_MARK(5)
@@ -478,9 +514,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
                       grow0 + (t0 + wg + (i - 1 + NST) * NWG) * TF32_TILE, &bar_tma[wg][nn % NST]);
         }
  if (!ABL(4))
-#pragma unroll
-        for (int j = 0; j < H; ++j)
-          asm volatile("st.shared.f32 [%0], %1;" ::"r"(e_ptr[j & 7] + (uint32_t)(j * 128)), "f"(z[j]) : "memory");
+          store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
         fence_proxy_async_smem();
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
@@ -494,7 +528,12 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       tc_fence_after();
       float* sc = reinterpret_cast<float*>(xb + wg * NST * G::TILE_BYTES);
 #pragma unroll
-      for (int j = 0; j < H; ++j) sc[wtid * (H + 1) + j] = dw1[j];
+      for (int j = 0; j < H; j += 2) {
+        float a, b;
+        unpack2(dw1p[j >> 1], a, b);
+        sc[wtid * (H + 1) + j] = a;
+        sc[wtid * (H + 1) + j + 1] = b;
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         db1 += __shfl_xor_sync(0xffffffffu, db1, o);
