@@ -164,6 +164,54 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
+    """BASELINE configs[1]: one window, TF32, rows sharded 58368/N per GPU, a P+1-double all-reduce
+    after every gradient launch.  Latency-bound: expected to get slower with more GPUs."""
+    from mcmc_bnn_example_b200.sharding import row_block
+    prec = m.PREC_TF32 if args.precision == "tf32" else m.PREC_FP32
+    K, W = args.steps, max(args.warmup, 3)
+    x, y, _ = m.synth_window(SEED, 0, ROWS)
+    r0, r1 = row_block(rank, world, ROWS)
+    cfg = m.baseline_config(precision=prec, seed=SEED, sample_capacity=0, leapfrog_steps=LEAPFROG, eps0=EPS)
+    ctx = m.Context(cfg, n_windows=1, rows=r1 - r0, device=local_rank)
+    if world > 1:
+        uid = [m.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        ctx.enable_row_sharding(uid[0], rank, world)
+    ctx.set_window_data(0, x[r0:r1], y[r0:r1], global_window=0)
+    stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    ctx.run_chain(W)
+    ctx.launch_count(reset=True)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    ctx.run_chain(K, sync=False)
+    e1.record(stream)
+    ctx.synchronize()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    launches = ctx.launch_count()
+    ctx.close()
+    if dist is not None:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": K / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": args.precision, "data": "synthetic",
+            "config": {"workload": "BASELINE configs[1]: 1 window x 58368 rows, rows sharded over GPUs, "
+                                   "all-reduce of 962 doubles per leapfrog step", "rows_per_gpu": r1 - r0,
+                       "leapfrog_steps": LEAPFROG, "us_per_gradient": 1e3 * ms / (K * LEAPFROG)},
+            "gpu_launches": launches}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -172,6 +220,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--windows", type=int, default=WINDOWS, help="total windows over all GPUs")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
+    ap.add_argument("--mode", default="windows", choices=["windows", "rows"],
+                    help="windows: configs[2], windows sharded over GPUs (the headline); rows: configs[1], ONE "
+                         "window whose rows are sharded, one NCCL all-reduce per leapfrog step")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -195,6 +246,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     n_gpus = world
 
+    if args.mode == "rows":
+        return run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev)
     # windows are independent: rank r takes the contiguous block of global windows [w0, w1)
     from mcmc_bnn_example_b200.sharding import window_block
     w0, w1 = window_block(rank, world, args.windows)

@@ -91,6 +91,7 @@ struct mcmc_b200_ctx {
   int device = 0, W = 0, P = 0, Pp = 0;
   long long rows = 0, rows_pad = 0;
   int num_sms = 0, ctas_per_sm = 1;
+  bool use_red = false, use_red_x = false;  // sum partial slots with a separate small launch
   int slices = 1;      // CTAs per window in chain launches
   int slices_x = 1;    // CTAs for single-window explicit calls
   int tile_rows = 64;
@@ -306,6 +307,10 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
     c->slices_x = (int)sx;
   }
 
+  // many slots per window (few windows per GPU): one small launch sums them once per step instead of
+  // every CTA of the next launch summing all of them in its prologue
+  c->use_red = c->slices > 8;
+  c->use_red_x = c->slices_x > 8;
   const size_t W = n_windows, Pp = c->Pp, P = c->P;
   DA(c->xaug, W * c->rows_pad * KP * sizeof(float));
   for (int i = 0; i < 2; ++i) {
@@ -532,7 +537,7 @@ static void fill_chain_accept(mcmc_b200_ctx* c, AcceptParams& a, int mode, int L
   const int last = (mode == ACC_BOOTSTRAP) ? 0 : (L - 1) & 1;
   a.partial = c->partial[last];
   a.ll_partial = c->llp[last];
-  a.red_in = c->comm ? c->red : nullptr;
+  a.red_in = (c->comm || c->use_red) ? c->red : nullptr;
   a.w_new = (mode == ACC_BOOTSTRAP) ? c->wbuf[0] : c->wbuf[L & 1];
   a.m_new = (mode == ACC_BOOTSTRAP) ? c->mbuf[0] : c->mbuf[L & 1];
   a.m0 = c->m0;
@@ -571,19 +576,22 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   g.m_out = c->mbuf[(s + 1) & 1];
   g.g_carried = c->g_cur;
   g.partial_in = c->partial[(s + 1) & 1];
-  g.red_in = (c->comm && mode == MODE_NEXT) ? c->red : nullptr;
+  const bool red = c->comm || c->use_red;
+  g.red_in = (red && mode == MODE_NEXT) ? c->red : nullptr;
   g.partial_out = c->partial[s & 1];
   g.ll_out = c->llp[s & 1];
   g.eps = c->eps;
   int r = launch_grad(c, g, false, st, (g.ablate & 512) ? c->dbg : nullptr);
   if (r) return r;
-  if (c->comm) {
+  if (red) {
     cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->tab_nslot, c->P,
                                            c->Pp, c->red, c->W, st);
     c->launches++;
     if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
-    r = allreduce(c, c->red, (size_t)c->W * (c->Pp + 4), st);
-    if (r) return r;
+    if (c->comm) {
+      r = allreduce(c, c->red, (size_t)c->W * (c->Pp + 4), st);
+      if (r) return r;
+    }
   }
   return MCMC_B200_OK;
 }
@@ -662,7 +670,7 @@ API int mcmc_b200_run_chain_async(mcmc_b200_ctx* c, int n_iter) {
     cudaGetLastError();
     c->launches = launches_before;
   }
-  const long long per_iter = (long long)c->cfg.leapfrog_steps * (c->comm ? 2 : 1) + 1;
+  const long long per_iter = (long long)c->cfg.leapfrog_steps * ((c->comm || c->use_red) ? 2 : 1) + 1;
   for (int i = 0; i < n_iter; ++i) {
     if (c->graph_exec) {
       CK(cudaGraphLaunch(c->graph_exec, c->stream));
@@ -752,7 +760,8 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
     g.m_out = (last && m_last) ? m_last : c->xm[(s + 1) & 1];
     g.g_carried = g0;
     g.partial_in = c->xpartial[(s + 1) & 1];
-    g.red_in = (c->comm && g.mode == MODE_NEXT) ? c->xred : nullptr;
+    const bool red = c->comm || c->use_red_x;
+    g.red_in = (red && g.mode == MODE_NEXT) ? c->xred : nullptr;
     g.partial_out = c->xpartial[s & 1];
     g.ll_out = c->xllp[s & 1];
     g.eps = nullptr;
@@ -761,13 +770,15 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
     g.row_loss_stride = 0;
     int r = launch_grad(c, g, true, st, (eval_only && c->cfg.precision == MCMC_B200_PREC_TF32) ? c->dbg : nullptr);
     if (r) return r;
-    if (c->comm) {
+    if (red) {
       cudaError_t e = launch_reduce_partials(c->xpartial[s & 1], c->xllp[s & 1], S, c->xtab_nslot, c->P, c->Pp,
                                              c->xred, 1, st);
       c->launches++;
       if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
-      r = allreduce(c, c->xred, (size_t)(c->Pp + 4), st);
-      if (r) return r;
+      if (c->comm) {
+        r = allreduce(c, c->xred, (size_t)(c->Pp + 4), st);
+        if (r) return r;
+      }
     }
   }
   AcceptParams a = base_accept_params(c);
@@ -776,7 +787,7 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
   a.nslot = c->xtab_nslot;
   a.partial = c->xpartial[(L - 1) & 1];
   a.ll_partial = c->xllp[(L - 1) & 1];
-  a.red_in = c->comm ? c->xred : nullptr;
+  a.red_in = (c->comm || c->use_red_x) ? c->xred : nullptr;
   a.w_new = eval_only ? w0 : ((w_last) ? w_last : c->xw[L & 1]);
   a.g_out = g_out;
   a.prior_loss_out = prior_loss;

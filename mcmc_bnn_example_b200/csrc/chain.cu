@@ -171,34 +171,58 @@ cudaError_t launch_repack(const float* x, const float* y, float* out, long long 
   return cudaGetLastError();
 }
 
-// ---- row sharding: this rank's sums, as doubles, ready for the allreduce ---
-__global__ void reduce_partials_kernel(const float* __restrict__ partial,
-                                       const double* __restrict__ ll_partial, int slices,
-                                       const int* __restrict__ nslot, int P, int Pp,
-                                       double* __restrict__ red) {
+// ---- sum of a window's partial vectors, as doubles ------------------------------
+// Used (a) when many CTAs touch one window (few windows per GPU): one small launch sums the
+// slots once instead of every CTA of the next launch summing all of them in its prologue, and
+// (b) for row sharding, where the result is what is all-reduced.  Fixed order: deterministic.
+constexpr int RED_PARAMS = 32, RED_GROUPS = 8;
+__global__ void __launch_bounds__(RED_PARAMS* RED_GROUPS)
+reduce_partials_kernel(const float* __restrict__ partial, const double* __restrict__ ll_partial, int slices,
+                       const int* __restrict__ nslot, int P, int Pp, double* __restrict__ red) {
+  __shared__ float sg[RED_GROUPS][RED_PARAMS];
+  __shared__ double sl[RED_GROUPS];
   const int win = blockIdx.y;
   const int ns = nslot ? nslot[win] : slices;
-  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  const int pi = threadIdx.x % RED_PARAMS, gi = threadIdx.x / RED_PARAMS;
+  const int p = blockIdx.x * RED_PARAMS + pi;
   double* r = red + (size_t)win * (Pp + 4);
+  float g = 0.f;
   if (p < P) {
-    const float* pi = partial + (size_t)win * slices * Pp + p;
-    float g = 0.f;
-    for (int s = 0; s < ns; ++s) g += pi[(size_t)s * Pp];
-    r[p] = (double)g;
-  } else if (p == Pp) {
-    double s = 0.0;
-    for (int i = 0; i < ns; ++i) s += ll_partial[(size_t)win * slices + i];
-    r[Pp] = s;
-  } else if (p < Pp + 4) {
-    r[p] = 0.0;
+    const float* src = partial + (size_t)win * slices * Pp + p;
+    for (int s = gi; s < ns; s += RED_GROUPS) g += src[(size_t)s * Pp];
+  }
+  sg[gi][pi] = g;
+  if (blockIdx.x == 0 && pi == 0) {
+    double l = 0.0;
+    for (int s = gi; s < ns; s += RED_GROUPS) l += ll_partial[(size_t)win * slices + s];
+    sl[gi] = l;
+  }
+  __syncthreads();
+  if (gi == 0) {
+    if (p < P) {
+      float t = sg[0][pi];
+#pragma unroll
+      for (int k = 1; k < RED_GROUPS; ++k) t += sg[k][pi];
+      r[p] = (double)t;
+    } else if (p < Pp) {
+      r[p] = 0.0;
+    }
+    if (blockIdx.x == 0 && pi == 0) {
+      double t = sl[0];
+#pragma unroll
+      for (int k = 1; k < RED_GROUPS; ++k) t += sl[k];
+      r[Pp] = t;
+      r[Pp + 1] = r[Pp + 2] = r[Pp + 3] = 0.0;
+    }
   }
 }
 
 cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices,
                                    const int* nslot, int P, int Pp, double* red, int windows,
                                    cudaStream_t st) {
-  dim3 grid((Pp + 4 + 255) / 256, windows);
-  reduce_partials_kernel<<<grid, 256, 0, st>>>(partial, ll_partial, slices, nslot, P, Pp, red);
+  dim3 grid((Pp + RED_PARAMS - 1) / RED_PARAMS, windows);
+  reduce_partials_kernel<<<grid, RED_PARAMS * RED_GROUPS, 0, st>>>(partial, ll_partial, slices, nslot, P, Pp,
+                                                                  red);
   return cudaGetLastError();
 }
 

@@ -49,7 +49,11 @@
 namespace mcmc_b200 {
 
 constexpr int TF32_NWG = 3;                            // compute warpgroups
-constexpr int TF32_THREADS = TF32_NWG * 128 + TF32_NWG * 32;  // + one control warp per warpgroup
+constexpr int TF32_THREADS = TF32_NWG * 128 + 128;      // + a control warpgroup (one warp per compute warpgroup, one idle)
+// registers: 512 threads start with 128 each; the control warpgroup hands most of its share to the
+// compute warpgroups (3 * 128 * 152 + 128 * 56 = 65536)
+constexpr int TF32_COMPUTE_REGS = 152;
+constexpr int TF32_CTRL_REGS = 56;
 constexpr int TF32_NST = 3;                            // TMA stages per warpgroup
 
 template <int H>
@@ -248,6 +252,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   constexpr int D = G::D, NF = G::NF, MB = G::MB, NB = G::NB, NWG = TF32_NWG, NST = TF32_NST;
   constexpr uint32_t IDESC_FWD = umma_idesc_tf32(128, NF, 0, 0);
   constexpr uint32_t IDESC_BWD = umma_idesc_tf32(MB, NB, 0, 1);
+  constexpr int NCOMPUTE = NWG * 128;
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base =
@@ -257,7 +262,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   unsigned char* w0s = es + G::ES_BYTES;      // [NF][128 B] weights, K-major, 16-byte-chunk swizzle
   float* w1s = reinterpret_cast<float*>(w0s + G::W0S_BYTES);
   __shared__ __align__(8) uint64_t bar_tma[NWG][NST];
-  __shared__ __align__(8) uint64_t bar_a[NWG], bar_fwd[NWG], bar_e[NWG], bar_bwd[NWG], bar_seg;
+  __shared__ __align__(8) uint64_t bar_fwd[NWG], bar_bwd[NWG];
   __shared__ uint32_t tmem_slot;
   __shared__ float b1s;
   __shared__ float red_w1[NWG][H];
@@ -282,12 +287,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   if (tid == 0) {
     for (int w = 0; w < NWG; ++w) {
       for (int s = 0; s < NST; ++s) mbar_init(&bar_tma[w][s], 1);
-      mbar_init(&bar_a[w], 128);
       mbar_init(&bar_fwd[w], 1);
-      mbar_init(&bar_e[w], 128);
       mbar_init(&bar_bwd[w], 1);
     }
-    mbar_init(&bar_seg, 1);
     mbar_fence_init();
   }
   // zero the weight operand once (rows >= H and k >= 23 stay zero)
@@ -299,114 +301,134 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   const uint32_t tmem = tmem_slot;
   const uint32_t tmem_g = tmem + G::G_COL0;
   const uint32_t w0s_addr = smem_u32(w0s);
-
-  // per-warpgroup tile counters over the whole launch: the mbarrier phases follow them
-  uint32_t n_done = 0;                        // compute threads: tiles this warpgroup has finished
-  uint32_t c_issued = 0;                      // control threads: tiles whose MMAs have been issued
-  uint32_t seg_count = 0;
+  const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];
   bool ok = true;
 
-  const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];
-  for (int sg = seg0; sg < seg1; ++sg, ++seg_count) {
-    const int4 seg = g.segs[sg];
-    const int win = seg.x, t0 = seg.y, t1 = seg.z, slot = seg.w;
-    const int nt = t1 - t0;
-    const int grow0 = (g.data_window0 + win) * rows_pad;  // first row of this window in the tensor map
-
-    // ---- segment prologue: start the first row tiles, fused leapfrog update, stage W0a ----
-    const int my_nt = is_ctrl ? 0 : (nt - wg + NWG - 1) / NWG;  // tiles t0 + wg, t0 + wg + NWG, ...
-    if (!is_ctrl && wtid == 0 && !ABL(256)) {
-      for (int i = 0; i < NST && i < my_nt; ++i) {
-        const uint32_t n = n_done + i;
-        mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
-        tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
-                    grow0 + (t0 + wg + i * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
-      }
-    }
-    // element (n = hidden unit, k) of the K-major B operand at n*128 + ((k/4) ^ (n%8))*16 + (k%4)*4
-    for (int p = tid; p < G::P; p += TF32_THREADS) {
-      const float w = leapfrog_param(g, win, p, slot == 0);
-      if (p < D * H + H) {
-        const int k = p / H, n = p - k * H;
-        *reinterpret_cast<float*>(w0s + n * 128 + (((k >> 2) ^ (n & 7)) << 4) + ((k & 3) << 2)) = w;
-      } else if (p < D * H + 2 * H) {
-        w1s[p - (D * H + H)] = w;
-      } else {
-        b1s = w;
-      }
-    }
-    fence_proxy_async_smem();
-    __syncthreads();
-
-    if (is_ctrl) {
-      // ---- control warp of warpgroup `wg`: waits on the warpgroup's hardware barriers with all 32
-      //      lanes, lane 0 issues.  Order per tile n: forward(n+1) as soon as its rows are in tensor
-      //      memory (the warpgroup stages them at the START of tile n), backward(n) when E(n) is in
-      //      shared memory; forward accumulators alternate between two buffers. ----
-      const int cnt = (nt - wg + NWG - 1) / NWG;
-      const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
-      const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE;
-      const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
-      const uint32_t ea = smem_u32(es + wg * G::ES_WG_BYTES);
-      auto issue_fwd = [&](uint32_t n) {
-        named_sync(BAR_ROWS0 + wg, 160);
-        if (lane == 0) {
-          tc_fence_after();
-          const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
-          if (!ABL(32))
+  // Every segment has three CTA-wide barriers, executed by both roles:
+  //   S1 parameters staged   S2 all tiles of the segment done   S3 read-out done
+  if (is_ctrl) {
+    // =====================  control warpgroup (warps 12..15; warp 15 only keeps the barriers) ==========
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TF32_CTRL_REGS));
+    uint32_t c_issued = 0;  // tiles of this warpgroup whose MMAs have been issued (mbarrier phases follow it)
+    for (int sg = seg0; sg < seg1; ++sg) {
+      const int4 seg = g.segs[sg];
+      const int win = seg.x, t0 = seg.y, nt = seg.z - seg.y;
+      const int grow0 = (g.data_window0 + win) * rows_pad;
+      __syncthreads();  // S1
+      if (wg < NWG) {
+        // Order per tile n: forward(n+1) as soon as its rows are in tensor memory (the warpgroup stages
+        // them at the START of tile n), backward(n) when E(n) is in shared memory, then — once those
+        // MMAs have completed — the TMA refill of the row stage they read.
+        const int cnt = (nt - wg + NWG - 1) / NWG;
+        const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
+        const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE;
+        const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
+        const uint32_t ea = smem_u32(es + wg * G::ES_WG_BYTES);
+        auto issue_fwd = [&](uint32_t n) {
+          named_sync(BAR_ROWS0 + wg, 160);
+          if (lane == 0) {
+            tc_fence_after();
+            const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
+            if (!ABL(32))
 #pragma unroll
-          for (int kb = 0; kb < 3; ++kb)
-            tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_k128(w0s_addr + kb * 32), IDESC_FWD, kb > 0);
-          tc_commit(&bar_fwd[wg]);
-        }
-        __syncwarp();
-      };
-      if (cnt > 0) issue_fwd(c_issued);
-      for (int i = 0; i < cnt; ++i) {
-        const uint32_t n = c_issued + i;
-        if (i + 1 < cnt) issue_fwd(n + 1);
-        named_sync(BAR_E0 + wg, 160);
-        if (lane == 0) {
-          tc_fence_after();
-          const uint32_t xa = smem_u32(xb + (wg * NST + n % NST) * G::TILE_BYTES);
-          if (!ABL(1))
+            for (int kb = 0; kb < 3; ++kb)
+              tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_k128(w0s_addr + kb * 32), IDESC_FWD, kb > 0);
+            tc_commit(&bar_fwd[wg]);
+          }
+          __syncwarp();
+        };
+        if (cnt > 0) issue_fwd(c_issued);
+        for (int i = 0; i < cnt; ++i) {
+          const uint32_t n = c_issued + i;
+          if (i + 1 < cnt) issue_fwd(n + 1);
+          named_sync(BAR_E0 + wg, 160);
+          if (lane == 0) {
+            tc_fence_after();
+            const uint32_t xa = smem_u32(xb + (wg * NST + n % NST) * G::TILE_BYTES);
+            if (!ABL(1))
 #pragma unroll
-          for (int kb = 0; kb < TF32_TILE / 8; ++kb)
-            tc_mma_tf32_ss(g_t, umma_desc_k128(ea + (kb >> 2) * G::ES_ATOM_BYTES + (kb & 3) * 32),
-                           umma_desc_mn32(xa + kb * 1024, G::TILE_BYTES), IDESC_BWD,
-                           (i == 0 && kb == 0) ? 0u : 1u);
-          tc_commit(&bar_bwd[wg]);
-          // this tile's row stage is free as soon as those MMAs have completed: refill it with the
-          // tile NST ahead right then (a full tile of lead for the copy)
-          if (i + NST < cnt && !ABL(256) && !ABL(1024)) {
-            ok = ok && mbar_wait(&bar_bwd[wg], n & 1, g.status, 213);
-            if (ok) {
-              mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
-              tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
-                          grow0 + (t0 + wg + (i + NST) * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+            for (int kb = 0; kb < TF32_TILE / 8; ++kb)
+              tc_mma_tf32_ss(g_t, umma_desc_k128(ea + (kb >> 2) * G::ES_ATOM_BYTES + (kb & 3) * 32),
+                             umma_desc_mn32(xa + kb * 1024, G::TILE_BYTES), IDESC_BWD,
+                             (i == 0 && kb == 0) ? 0u : 1u);
+            tc_commit(&bar_bwd[wg]);
+            if (i + NST < cnt && !ABL(256)) {
+              ok = ok && mbar_wait(&bar_bwd[wg], n & 1, g.status, 213);
+              if (ok) {
+                mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
+                tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
+                            grow0 + (t0 + wg + (i + NST) * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+              }
             }
           }
+          __syncwarp();
         }
-        __syncwarp();
+        c_issued += cnt;
       }
-      c_issued += cnt;
-    } else {
-      // ---- compute warpgroup: one row per thread ----
+      __syncthreads();  // S2
+      __syncthreads();  // S3
+    }
+  } else {
+    // =====================  compute warpgroups: one row per thread  =====================================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TF32_COMPUTE_REGS));
+    uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
+    const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
+    const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
+    const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE + lane_off;
+    // E element (hidden j, row r): atom r/32 (= this warp), line j, 16-byte chunk (r%32)/4 ^ (j%8)
+    uint32_t e_ptr[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c)
+      e_ptr[c] = smem_u32(es + wg * G::ES_WG_BYTES + wwarp * G::ES_ATOM_BYTES) +
+                 ((uint32_t)(((lane >> 2) ^ c) << 4)) + ((lane & 3) << 2);
+    // rows r and r+4 of a staged tile keep their 32-byte chunks in the same banks: the upper four of
+    // every eight rows read the two halves of a chunk in the opposite order
+    const bool swap_halves = (wtid & 4) != 0;
+
+    for (int sg = seg0; sg < seg1; ++sg) {
+      const int4 seg = g.segs[sg];
+      const int win = seg.x, t0 = seg.y, t1 = seg.z, slot = seg.w;
+      const int nt = t1 - t0;
+      const int grow0 = (g.data_window0 + win) * rows_pad;  // first row of this window in the tensor map
+      const int my_nt = (nt - wg + NWG - 1) / NWG;          // tiles t0 + wg, t0 + wg + NWG, ...
+
+      // ---- segment prologue: start the first row tiles, fused leapfrog update, stage W0a ----
+      if (wtid == 0 && !ABL(256)) {
+        for (int i = 0; i < NST && i < my_nt; ++i) {
+          const uint32_t n = n_done + i;
+          mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
+          tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
+                      grow0 + (t0 + wg + i * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+        }
+      }
+      // element (n = hidden unit, k) of the K-major B operand at n*128 + ((k/4) ^ (n%8))*16 + (k%4)*4
+      for (int p = tid; p < G::P; p += NCOMPUTE) {
+        const float w = leapfrog_param(g, win, p, slot == 0);
+        if (p < D * H + H) {
+          const int k = p / H, n = p - k * H;
+          *reinterpret_cast<float*>(w0s + n * 128 + (((k >> 2) ^ (n & 7)) << 4) + ((k & 3) << 2)) = w;
+        } else if (p < D * H + 2 * H) {
+          w1s[p - (D * H + H)] = w;
+        } else {
+          b1s = w;
+        }
+      }
+      fence_proxy_async_smem();
+      __syncthreads();  // S1
+
+      // output-layer weights live in registers for the whole segment
+      float w1r[H];
+#pragma unroll
+      for (int j = 0; j < H; j += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(w1s + j);
+        w1r[j] = v.x; w1r[j + 1] = v.y; w1r[j + 2] = v.z; w1r[j + 3] = v.w;
+      }
+      const float b1 = b1s;
       uint64_t dw1p[H / 2];  // dW1 accumulators, two hidden units per register pair
 #pragma unroll
       for (int j = 0; j < H / 2; ++j) dw1p[j] = 0ull;
       float db1 = 0.f;
       double llacc = 0.0;
-      const float b1 = b1s;
-      const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
-      const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
-      const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE + lane_off;
-      // E element (hidden j, row r): atom r/32 (= this warp), line j, 16-byte chunk (r%32)/4 ^ (j%8)
-      uint32_t e_ptr[8];
-#pragma unroll
-      for (int c = 0; c < 8; ++c)
-        e_ptr[c] = smem_u32(es + wg * G::ES_WG_BYTES + wwarp * G::ES_ATOM_BYTES) +
-                   ((uint32_t)(((lane >> 2) ^ c) << 4)) + ((lane & 3) << 2);
 
       // hands this thread's row of the landed tile to the tensor core (forward A operand); returns y
       auto stage_row = [&](uint32_t n) -> float {
@@ -418,15 +440,23 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
           const unsigned char* cp = xrow + ((j ^ (wtid & 3)) << 5);
-          xr[2 * j] = *reinterpret_cast<const float4*>(cp);
-          xr[2 * j + 1] = *reinterpret_cast<const float4*>(cp + 16);
+          const float4 first = *reinterpret_cast<const float4*>(cp + (swap_halves ? 16 : 0));
+          const float4 second = *reinterpret_cast<const float4*>(cp + (swap_halves ? 0 : 16));
+          xr[2 * j].x = swap_halves ? second.x : first.x;
+          xr[2 * j].y = swap_halves ? second.y : first.y;
+          xr[2 * j].z = swap_halves ? second.z : first.z;
+          xr[2 * j].w = swap_halves ? second.w : first.w;
+          xr[2 * j + 1].x = swap_halves ? first.x : second.x;
+          xr[2 * j + 1].y = swap_halves ? first.y : second.y;
+          xr[2 * j + 1].z = swap_halves ? first.z : second.z;
+          xr[2 * j + 1].w = swap_halves ? first.w : second.w;
         }
         if (!ABL(64))
 #pragma unroll
         for (int j = 0; j < 3; ++j) tc_st8(a_t + j * 8, xr[2 * j], xr[2 * j + 1]);
         return xr[5].w;
       };
-      // ... and tells the control thread once the stores have landed
+      // ... and tells the control warp once the stores have landed
       auto publish_row = [&]() {
         tc_wait_st();
         tc_fence_before();
@@ -455,11 +485,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         float z[H];
         if (!ABL(128)) {
 #pragma unroll
-        for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
-        tc_wait_ld();
+          for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
+          tc_wait_ld();
         } else {
 #pragma unroll
-        for (int c = 0; c < H; ++c) z[c] = 0.01f * c;
+          for (int c = 0; c < H; ++c) z[c] = 0.01f * c;
         }
         PROF_MARK(2)
         if (i + 1 < my_nt) publish_row();
@@ -470,18 +500,16 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           dbg[wtid * 64 + 63] = y;
         }
         float pred = b1;
-        if (!ABL(8))
+        if (!ABL(8)) {
+          float pred1 = 0.f;
 #pragma unroll
-        for (int j = 0; j < H; j += 4) {
-          const float4 w1v = *reinterpret_cast<const float4*>(w1s + j);
-          z[j] = tanh_fast(z[j]);
-          z[j + 1] = tanh_fast(z[j + 1]);
-          z[j + 2] = tanh_fast(z[j + 2]);
-          z[j + 3] = tanh_fast(z[j + 3]);
-          pred = fmaf(w1v.x, z[j], pred);
-          pred = fmaf(w1v.y, z[j + 1], pred);
-          pred = fmaf(w1v.z, z[j + 2], pred);
-          pred = fmaf(w1v.w, z[j + 3], pred);
+          for (int j = 0; j < H; j += 2) {
+            z[j] = tanh_fast(z[j]);
+            z[j + 1] = tanh_fast(z[j + 1]);
+            pred = fmaf(w1r[j], z[j], pred);
+            pred1 = fmaf(w1r[j + 1], z[j + 1], pred1);
+          }
+          pred += pred1;
         }
         PROF_MARK(4)
         const int grow = t * TF32_TILE + wtid;
@@ -503,18 +531,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
             unpack2(e2, z[j], z[j + 1]);
           }
         }
-        // the previous tile's backward MMAs must be done with E before it is overwritten
         PROF_MARK(5)
+        // the previous tile's backward MMAs must be done with E before it is overwritten
         if (n > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n - 1) & 1, g.status, 203);
         PROF_MARK(6)
-        if (wtid == 0 && i >= 1 && i - 1 + NST < my_nt && ok && ABL(1024)) {
-          const uint32_t nn = n - 1 + NST;
-          mbar_expect_tx(&bar_tma[wg][nn % NST], G::TILE_BYTES);
-          tma_load_2d(xb + (wg * NST + nn % NST) * G::TILE_BYTES, &tmap_mn, 0,
-                      grow0 + (t0 + wg + (i - 1 + NST) * NWG) * TF32_TILE, &bar_tma[wg][nn % NST]);
-        }
- if (!ABL(4))
-          store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
+        if (!ABL(4)) store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
         fence_proxy_async_smem();
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
@@ -543,65 +564,65 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         red_db1[warp] = db1;
         red_ll[warp] = llacc;
       }
-      asm volatile("bar.sync %0, 128;" ::"r"(wg + 1) : "memory");  // this warpgroup only
+      named_sync(wg + 1, 128);  // this warpgroup only
       if (wtid < H) {
         float s = 0.f;
         for (int r = 0; r < 128; ++r) s += sc[r * (H + 1) + wtid];
         red_w1[wg][wtid] = s;
       }
-    }
-    __syncthreads();
+      __syncthreads();  // S2
 
-    // ---- segment read-out: one partial gradient vector for (window, slot) ----
-    float* po = g.partial_out + ((size_t)win * g.slices_out + slot) * g.Pp;
-    if (warp < 4) {
-      tc_fence_after();
-      float gacc[NB];
-      const uint32_t trow = tmem_g + ((uint32_t)(warp * 32) << 16);
+      // ---- segment read-out: one partial gradient vector for (window, slot) ----
+      float* po = g.partial_out + ((size_t)win * g.slices_out + slot) * g.Pp;
+      if (warp < 4) {
+        tc_fence_after();
+        float gacc[NB];
+        const uint32_t trow = tmem_g + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
-      for (int c = 0; c < NB; c += 8) tc_ld8(trow + c, gacc + c);
-      tc_wait_ld();
-      // the other warpgroups' accumulators (those that had tiles in this segment)
+        for (int c = 0; c < NB; c += 8) tc_ld8(trow + c, gacc + c);
+        tc_wait_ld();
+        // the other warpgroups' accumulators (those that had tiles in this segment)
 #pragma unroll
-      for (int w = 1; w < NWG; ++w) {
-        if (w < nt) {
-          float g2[NB];
+        for (int w = 1; w < NWG; ++w) {
+          if (w < nt) {
+            float g2[NB];
 #pragma unroll
-          for (int c = 0; c < NB; c += 8) tc_ld8(trow + w * G::G_STRIDE + c, g2 + c);
-          tc_wait_ld();
+            for (int c = 0; c < NB; c += 8) tc_ld8(trow + w * G::G_STRIDE + c, g2 + c);
+            tc_wait_ld();
 #pragma unroll
-          for (int c = 0; c < NB; ++c) gacc[c] += g2[c];
+            for (int c = 0; c < NB; ++c) gacc[c] += g2[c];
+          }
+        }
+        if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0) {
+#pragma unroll
+          for (int c = 0; c < NB; ++c) dbg[8192 + tid * 32 + c] = gacc[c];
+        }
+        // M = 64: accumulator row i lives in lane 32*(i/16) + i%16
+        const int hidx = lane < 16 ? warp * 16 + lane : -1;
+        if (hidx >= 0 && hidx < H) {
+          const float w1 = w1s[hidx];
+#pragma unroll
+          for (int k = 0; k < D; ++k) po[k * H + hidx] = w1 * gacc[k];
+          po[D * H + hidx] = w1 * gacc[COL_ONE];
+        }
+        tc_fence_before();
+      } else if (warp == 4) {
+        for (int j = lane; j < H; j += 32) {
+          float s = red_w1[0][j];
+#pragma unroll
+          for (int w = 1; w < NWG; ++w) s += red_w1[w][j];
+          po[D * H + H + j] = s;
+        }
+        if (lane == 0) {
+          float s = 0.f;
+          double l = 0.0;
+          for (int w = 0; w < NWG * 4; ++w) { s += red_db1[w]; l += red_ll[w]; }
+          po[D * H + 2 * H] = s;
+          g.ll_out[(size_t)win * g.slices_out + slot] = l;
         }
       }
-      if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0) {
-#pragma unroll
-        for (int c = 0; c < NB; ++c) dbg[8192 + tid * 32 + c] = gacc[c];
-      }
-      // M = 64: accumulator row i lives in lane 32*(i/16) + i%16
-      const int hidx = lane < 16 ? warp * 16 + lane : -1;
-      if (hidx >= 0 && hidx < H) {
-        const float w1 = w1s[hidx];
-#pragma unroll
-        for (int k = 0; k < D; ++k) po[k * H + hidx] = w1 * gacc[k];
-        po[D * H + hidx] = w1 * gacc[COL_ONE];
-      }
-      tc_fence_before();
-    } else if (warp == 4) {
-      for (int j = lane; j < H; j += 32) {
-        float s = red_w1[0][j];
-#pragma unroll
-        for (int w = 1; w < NWG; ++w) s += red_w1[w][j];
-        po[D * H + H + j] = s;
-      }
-      if (lane == 0) {
-        float s = 0.f;
-        double l = 0.0;
-        for (int w = 0; w < NWG * 4; ++w) { s += red_db1[w]; l += red_ll[w]; }
-        po[D * H + 2 * H] = s;
-        g.ll_out[(size_t)win * g.slices_out + slot] = l;
-      }
+      __syncthreads();  // S3: read-out done before the next segment restages W0a / reuses the scratch
     }
-    __syncthreads();  // read-out done before the next segment restages W0a / reuses E
   }
 
   tc_fence_before();
