@@ -309,8 +309,8 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
 
   // many slots per window (few windows per GPU): one small launch sums them once per step instead of
   // every CTA of the next launch summing all of them in its prologue
-  c->use_red = c->slices > 8;
-  c->use_red_x = c->slices_x > 8;
+  c->use_red = c->slices > 4;
+  c->use_red_x = c->slices_x > 4;
   const size_t W = n_windows, Pp = c->Pp, P = c->P;
   DA(c->xaug, W * c->rows_pad * KP * sizeof(float));
   for (int i = 0; i < 2; ++i) {
