@@ -171,6 +171,87 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_reference_gpu(args):
+    """Same-box GPU baseline: the reference's own, unmodified FP32 (FFMA) kernels, built for sm_100a by
+    oracle/Makefile into oracle/_ref/libref_ffma.so (only where the reference tree was present at build
+    time), timed on ONE window at the shapes the reference fixes at compile time (58368 rows, Student-t,
+    10 leapfrog steps per call).  The reference has no window batching: 200 windows are 200 such runs.
+    Its TF32 kernel is never run (it reads past the end of the dataset and spins without a limit)."""
+    import ctypes as C
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    lib_path = os.path.join(ROOT, "oracle", "_ref", "libref_ffma.so")
+    if not os.path.exists(lib_path):
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "oracle/_ref/libref_ffma.so was not built "
+                          "(the reference tree is needed at build time)"}), flush=True)
+        return
+    import mcmc_bnn_example_b200 as m
+    ref = C.CDLL(lib_path)
+    x, y, _ = m.synth_window(SEED, 0, ROWS)
+    x = np.ascontiguousarray(x * np.float32(0.001))
+    us = C.c_float(0.0)
+    fp = lambda a: a.ctypes.data_as(C.POINTER(C.c_float))
+    rc = ref.ref_ffma_time_steps(fp(x), fp(np.ascontiguousarray(y)), C.c_float(1e-4), max(args.warmup, 3),
+                                 max(args.steps, 1), C.byref(us))
+    if rc != 0:
+        print(json.dumps({"impl": "reference_gpu", "unavailable": "harness returned %d" % rc}), flush=True)
+        return
+    grads = 1e6 / us.value
+    print(json.dumps({
+        "impl": "reference_gpu", "metric": "gradients_per_sec_one_window", "value": grads, "unit": "gradients/s",
+        "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 3), "us_per_gradient": us.value,
+        "samples_per_sec_equivalent": grads / LEAPFROG, "higher_is_better": True, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": "reference FFMA kernel (leapfrog_step_kernel), 1 window x 58368 rows, Student-t, "
+                               "mcmc_step<float,10>; a step here = one call = 10 gradients"}}), flush=True)
+
+
+def run_readme(args, m, torch, dev):
+    """The reference's own preset (README workload): Student-t(100, 2.2) likelihood, N(0, 200^2) prior,
+    L = 1000 leapfrog steps, adaptive step size, features scaled by 0.001 — on `--windows` windows batched
+    in one context.  Reports gradients/s and the projected time of 200 windows x 900 iterations, the
+    quantity the reference's README tabulates (42 min on one A100 with its TF32 kernel)."""
+    prec = m.PREC_TF32 if args.precision == "tf32" else m.PREC_FP32
+    W = args.windows
+    cfg = m.reference_config(precision=prec, sample_capacity=1, seed=SEED)
+    L = cfg.leapfrog_steps
+    ctx = m.Context(cfg, n_windows=W, rows=ROWS, device=dev.index)
+    for w in range(W):
+        x, y, _ = m.synth_window(SEED, w, ROWS)
+        ctx.set_window_data(w, x * np.float32(0.001), y, global_window=w)
+    ctx.run_chain(1)
+    ctx.synchronize()
+    K = max(1, min(args.steps, 5))
+    sampler = ClockSampler(dev.index)
+    sampler.start()
+    st = torch.cuda.ExternalStream(ctx.stream, device=dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n0 = ctx.launch_count()
+    with torch.cuda.stream(st):
+        e0.record(st)
+        ctx.run_chain(K, sync=False)
+        e1.record(st)
+    ctx.synchronize()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    launches = ctx.launch_count() - n0
+    grads = W * K * L / (ms * 1e-3)
+    out = {
+        "metric": "gradients_per_sec_all_windows", "value": grads, "unit": "gradients/s", "n_gpus": 1,
+        "steps": K, "warmup": 1, "ms_per_step": ms / K, "higher_is_better": True, "dtype": args.precision,
+        "data": "synthetic", "gpu_launches": launches, "clocks": clocks,
+        "config": {"workload": "reference preset (README): Student-t, N(0,200^2) prior, L=%d, adaptive eps, "
+                               "x scaled 1e-3; %d windows x %d rows batched" % (L, W, ROWS),
+                   "windows": W, "leapfrog_steps": L,
+                   "projected_minutes_200_windows_900_iterations": 200 * 900 * L / grads / 60.0,
+                   "reference_readme_minutes_1xA100_tf32": 42.0},
+        "roofline": {"bound": "hbm", "achieved": 92.0 * ROWS * grads / 1e9,
+                     "peak": measured_peaks()[0], "unit": "GB/s",
+                     "frac": 92.0 * ROWS * grads / 1e9 / measured_peaks()[0], "traffic": None},
+    }
+    print(json.dumps(out), flush=True)
+
+
 def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
     """BASELINE configs[1]: one window, TF32, rows sharded 58368/N per GPU, a P+1-double all-reduce
     after every gradient launch.  Latency-bound: expected to get slower with more GPUs."""
@@ -224,10 +305,10 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_gpu"])
     ap.add_argument("--windows", type=int, default=WINDOWS, help="total windows over all GPUs")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
-    ap.add_argument("--mode", default="windows", choices=["windows", "rows"],
+    ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme"],
                     help="windows: configs[2], windows sharded over GPUs (the headline); rows: configs[1], ONE "
                          "window whose rows are sharded, one NCCL all-reduce per leapfrog step")
     ap.add_argument("--no-e2e", action="store_true")
@@ -235,6 +316,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.impl == "reference_gpu":
+        return run_reference_gpu(args)
     args.warmup = max(args.warmup, 3)
 
     import torch
@@ -255,6 +338,10 @@ def main():
 
     if args.mode == "rows":
         return run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev)
+    if args.mode == "readme":
+        if rank == 0:
+            run_readme(args, m, torch, dev)
+        return
     # windows are independent: rank r takes the contiguous block of global windows [w0, w1)
     from mcmc_bnn_example_b200.sharding import window_block
     w0, w1 = window_block(rank, world, args.windows)

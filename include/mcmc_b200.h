@@ -177,6 +177,23 @@ int mcmc_b200_final_loss(mcmc_b200_ctx* ctx, int window, int first, int count, d
                          double* mean_logprior);
 
 /*
+ * Checkpoint / resume.  The reference keeps samples and chain state in device
+ * memory only and loses them when the process ends (main.h:183,277-283,295).
+ * A checkpoint is one host blob: a fixed header (configuration fingerprint,
+ * iterations done) followed by every window's position, momentum, carried
+ * gradient and energies, step size, counters, stored samples and trace.  The
+ * dataset is NOT part of it: upload every window's data (same global window
+ * ids) before loading.  Because every random draw is a pure function of
+ * (seed, global window, iteration), a resumed chain continues bit-identically.
+ *   size : bytes a save needs for this context
+ *   save : synchronises the context, writes the blob to host_buf
+ *   load : checks the header against this context's configuration, restores
+ */
+int mcmc_b200_checkpoint_size(mcmc_b200_ctx* ctx, uint64_t* bytes);
+int mcmc_b200_checkpoint_save(mcmc_b200_ctx* ctx, void* host_buf, uint64_t bytes);
+int mcmc_b200_checkpoint_load(mcmc_b200_ctx* ctx, const void* host_buf, uint64_t bytes);
+
+/*
  * Row sharding of ONE window over several GPUs (one process per GPU): every
  * rank holds rows/nranks rows, and each leapfrog step sums the P-vector of
  * gradient partials (plus the log-likelihood) over ranks with one NCCL

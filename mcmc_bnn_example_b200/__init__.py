@@ -38,6 +38,7 @@ EXPORTS = [
     "mcmc_b200_nccl_unique_id", "mcmc_b200_enable_row_sharding", "mcmc_b200_mcmc_step",
     "mcmc_b200_log_acpt", "mcmc_b200_synth_window", "mcmc_b200_philox_normal", "mcmc_b200_philox_raw",
     "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
+    "mcmc_b200_checkpoint_size", "mcmc_b200_checkpoint_save", "mcmc_b200_checkpoint_load",
 ]
 
 
@@ -281,6 +282,48 @@ class Context:
         a, b = C.c_double(), C.c_double()
         _check(lib().mcmc_b200_final_loss(self._h, window, first, count, C.byref(a), C.byref(b)))
         return a.value, b.value
+
+    # -- checkpoint / resume / export -----------------------------------------
+    def checkpoint(self):
+        """The chain state of every window (position, momentum, carried gradient, step size, counters,
+        stored samples, trace) as one bytes object; the dataset is not included."""
+        n = C.c_uint64()
+        _check(lib().mcmc_b200_checkpoint_size(self._h, C.byref(n)))
+        buf = np.empty(n.value, np.uint8)
+        _check(lib().mcmc_b200_checkpoint_save(self._h, buf.ctypes.data_as(C.c_void_p), n))
+        return buf
+
+    def restore(self, blob):
+        """Resume from ``checkpoint()`` output (same configuration, data already uploaded)."""
+        buf = np.ascontiguousarray(np.frombuffer(blob, np.uint8) if not isinstance(blob, np.ndarray) else blob)
+        _check(lib().mcmc_b200_checkpoint_load(self._h, buf.ctypes.data_as(C.c_void_p), C.c_uint64(buf.size)))
+
+    def save_checkpoint(self, path):
+        self.checkpoint().tofile(path)
+
+    def load_checkpoint(self, path):
+        self.restore(np.fromfile(path, np.uint8))
+
+    def export_samples(self, prefix, first=0, count=None):
+        """Writes ``prefix.samples.f32`` (raw little-endian float32 [windows][count][P]) and
+        ``prefix.json`` (shape, configuration, per-window counters and the recorded trace)."""
+        import json
+        count = self.cfg.sample_capacity - first if count is None else count
+        with open(prefix + ".samples.f32", "wb") as f:
+            for w in range(self.n_windows):
+                self.get_samples(w, first, count).tofile(f)
+        meta = {"shape": [self.n_windows, count, self.P], "dtype": "float32", "first_sample": first,
+                "config": {k: getattr(self.cfg, k) for k, _ in Config._fields_},
+                "windows": [self.chain_info(w) for w in range(self.n_windows)]}
+        if self.cfg.trace_iters > 0:
+            done = min(self.cfg.trace_iters, min(i["iterations"] for i in meta["windows"]))
+            meta["trace"] = []
+            for w in range(self.n_windows):
+                t = self.get_trace(w, 0, done)
+                meta["trace"].append({"log_u": t["log_u"].tolist(), "log_acpt": t["log_acpt"].tolist(),
+                                      "accepted": t["accepted"].tolist(), "eps": t["eps"].tolist()})
+        with open(prefix + ".json", "w") as f:
+            json.dump(meta, f)
 
     # -- multi-GPU -----------------------------------------------------------
     def enable_row_sharding(self, unique_id: bytes, rank, nranks):

@@ -742,6 +742,121 @@ API int mcmc_b200_get_trace(mcmc_b200_ctx* c, int window, int first, int count, 
   return MCMC_B200_OK;
 }
 
+// ---- checkpoint / resume ------------------------------------------------------
+// The reference keeps its samples in device memory and loses them, with the chain state, when the
+// process ends (main.h:183,277-283,295).  Every random draw here is a pure function of (seed, global
+// window, iteration), so a chain resumed from a checkpoint continues bit-identically.
+namespace {
+struct CkptHeader {
+  char magic[8];          // "MCB2CKPT"
+  uint32_t version, header_bytes;
+  int32_t W, P, Pp, D, H, likelihood, precision, leapfrog_steps, burn_in, adapt_steps, sample_capacity,
+      trace_iters, iters_done, slices;
+  int64_t rows;
+  uint64_t seed;
+  uint64_t payload_bytes;
+};
+struct CkptField {
+  void* dev;
+  size_t bytes;
+};
+std::vector<CkptField> ckpt_fields(mcmc_b200_ctx* c) {
+  const size_t W = c->W, Pp = c->Pp, P = c->P, S = c->cfg.sample_capacity, K = c->cfg.trace_iters;
+  std::vector<CkptField> f = {
+      {c->wbuf[0], W * Pp * 4}, {c->mbuf[0], W * Pp * 4}, {c->w_cur, W * Pp * 4}, {c->g_cur, W * Pp * 4},
+      {c->m0, W * Pp * 4},      {c->ll_cur, W * 8},       {c->lp_cur, W * 8},     {c->eps, W * 4},
+      {c->iter, W * 4},         {c->n_accept, W * 4},     {c->gwin, W * 8}};
+  if (c->samples) f.push_back({c->samples, W * S * P * 4});
+  if (K > 0) {
+    f.push_back({c->tr_mom, W * K * P * 4});
+    f.push_back({c->tr_log_u, W * K * 4});
+    f.push_back({c->tr_log_acpt, W * K * 8});
+    f.push_back({c->tr_accept, W * K * 4});
+    f.push_back({c->tr_eps, W * K * 4});
+  }
+  return f;
+}
+CkptHeader ckpt_header(mcmc_b200_ctx* c) {
+  CkptHeader h;
+  memset(&h, 0, sizeof h);
+  memcpy(h.magic, "MCB2CKPT", 8);
+  h.version = 1;
+  h.header_bytes = sizeof(CkptHeader);
+  h.W = c->W; h.P = c->P; h.Pp = c->Pp; h.D = c->cfg.D; h.H = c->cfg.H;
+  h.likelihood = c->cfg.likelihood; h.precision = c->cfg.precision;
+  h.leapfrog_steps = c->cfg.leapfrog_steps; h.burn_in = c->cfg.burn_in; h.adapt_steps = c->cfg.adapt_steps;
+  h.sample_capacity = c->cfg.sample_capacity; h.trace_iters = c->cfg.trace_iters;
+  h.iters_done = c->iters_done; h.slices = c->slices;
+  h.rows = c->rows; h.seed = c->cfg.seed;
+  for (const CkptField& f : ckpt_fields(c)) h.payload_bytes += f.bytes;
+  return h;
+}
+}  // namespace
+
+API int mcmc_b200_checkpoint_size(mcmc_b200_ctx* c, uint64_t* bytes) {
+  if (!c || !bytes) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  const CkptHeader h = ckpt_header(c);
+  *bytes = sizeof(CkptHeader) + h.payload_bytes;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_checkpoint_save(mcmc_b200_ctx* c, void* host_buf, uint64_t bytes) {
+  if (!c || !host_buf) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (!c->bootstrapped) return fail(MCMC_B200_ERR_INVALID, "nothing to save: the chain has not started");
+  CK(cudaSetDevice(c->device));
+  int r = check_status(c);  // synchronises; a chain that timed out is not worth saving
+  if (r) return r;
+  const CkptHeader h = ckpt_header(c);
+  if (bytes < sizeof(CkptHeader) + h.payload_bytes) return fail(MCMC_B200_ERR_INVALID, "buffer too small");
+  memcpy(host_buf, &h, sizeof h);
+  char* p = static_cast<char*>(host_buf) + sizeof h;
+  for (const CkptField& f : ckpt_fields(c)) {
+    CK(cudaMemcpy(p, f.dev, f.bytes, cudaMemcpyDeviceToHost));
+    p += f.bytes;
+  }
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_checkpoint_load(mcmc_b200_ctx* c, const void* host_buf, uint64_t bytes) {
+  if (!c || !host_buf || bytes < sizeof(CkptHeader)) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CkptHeader h;
+  memcpy(&h, host_buf, sizeof h);
+  const CkptHeader want = ckpt_header(c);
+  if (memcmp(h.magic, want.magic, 8) != 0 || h.version != want.version || h.header_bytes != sizeof h)
+    return fail(MCMC_B200_ERR_INVALID, "not a checkpoint of this library version");
+  if (h.W != want.W || h.P != want.P || h.Pp != want.Pp || h.D != want.D || h.H != want.H ||
+      h.likelihood != want.likelihood || h.precision != want.precision ||
+      h.leapfrog_steps != want.leapfrog_steps || h.burn_in != want.burn_in ||
+      h.adapt_steps != want.adapt_steps || h.sample_capacity != want.sample_capacity ||
+      h.trace_iters != want.trace_iters || h.rows != want.rows || h.seed != want.seed ||
+      h.payload_bytes != want.payload_bytes)
+    return fail(MCMC_B200_ERR_INVALID, "checkpoint was written by a context with a different configuration");
+  if (bytes < sizeof h + h.payload_bytes) return fail(MCMC_B200_ERR_INVALID, "truncated checkpoint");
+  for (int w = 0; w < c->W; ++w)
+    if (!c->window_set[w]) return fail(MCMC_B200_ERR_INVALID, "upload every window's data before resuming");
+  CK(cudaSetDevice(c->device));
+  CK(cudaStreamSynchronize(c->stream));
+  const char* p = static_cast<const char*>(host_buf) + sizeof h;
+  const std::vector<CkptField> fields = ckpt_fields(c);
+  // the stored global window ids must be the ones this context was given: chains are keyed by them
+  {
+    size_t off = 0;
+    for (const CkptField& f : fields) {
+      if (f.dev == c->gwin) break;
+      off += f.bytes;
+    }
+    if (memcmp(p + off, c->h_gwin.data(), (size_t)c->W * 8) != 0)
+      return fail(MCMC_B200_ERR_INVALID, "checkpoint belongs to other global windows");
+  }
+  for (const CkptField& f : fields) {
+    CK(cudaMemcpy(f.dev, p, f.bytes, cudaMemcpyHostToDevice));
+    p += f.bytes;
+  }
+  c->bootstrapped = true;
+  c->iters_done = h.iters_done;
+  return MCMC_B200_OK;
+}
+
 // ---- explicit-state calls (one window) -------------------------------------
 // L leapfrog steps from (w0, m0, g0) on device; results in xw/xm[L&1], g_out, scalars.
 static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, const float* w0,

@@ -100,3 +100,39 @@ REF_API int ref_log_acpt(const float* prev_loss, const float* new_loss, const fl
   if (tmp_storage) cudaFree(tmp_storage);
   return cudaGetLastError() == cudaSuccess ? 0 : 3;
 }
+
+// Device time of the reference's FFMA path: `reps` calls of mcmc_step<float, 10> (ten launches of
+// leapfrog_step_kernel each) on resident buffers, timed with CUDA events; returns the mean time of one
+// leapfrog step (= one full-batch gradient) in microseconds through *us_per_step.
+REF_API int ref_ffma_time_steps(const float* x, const float* y, float eps, int warmup, int reps,
+                                float* us_per_step) {
+  using namespace mcmc;
+  init_once();
+  cudaStream_t stream = cudaStreamPerThread;
+  DeviceMatrix<float> data(N_SAMPLES, N_COLS), labels(N_SAMPLES, 1);
+  h2d(data, x, (size_t)N_SAMPLES * N_COLS);
+  h2d(labels, y, (size_t)N_SAMPLES);
+  const int NP = N_P_ALIGNED;
+  DeviceMatrix<float> block(7, NP, 0.f, stream);
+  DeviceMatrix<float> wp(1, NP, block.ptr()), mp(1, NP, block.ptr() + NP), gp(1, NP, block.ptr() + 2 * NP),
+      wn(1, NP, block.ptr() + 3 * NP), gc(1, NP, block.ptr() + 4 * NP), gn(1, NP, block.ptr() + 5 * NP),
+      mn(1, NP, block.ptr() + 6 * NP);
+  DeviceMatrix<float> loss(1, N_SAMPLES + NUM_PARAMS, 0.f, stream);
+  cudaStreamSynchronize(stream);
+  cudaEvent_t e0, e1;
+  cudaEventCreate(&e0);
+  cudaEventCreate(&e1);
+  for (int r = 0; r < warmup + reps; ++r) {
+    if (r == warmup) cudaEventRecord(e0, stream);
+    cudaMemsetAsync(gc.ptr(), 0, NP * sizeof(float), stream);  // the step expects a zeroed grad_cur
+    mcmc_step<float, 10>(data, labels, wp, wn, mp, mn, gp, gc, gn, loss, nullptr, eps, stream);
+  }
+  cudaEventRecord(e1, stream);
+  if (cudaStreamSynchronize(stream) != cudaSuccess) return 2;
+  float ms = 0.f;
+  cudaEventElapsedTime(&ms, e0, e1);
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *us_per_step = ms * 1000.f / (10.f * reps);
+  return cudaGetLastError() == cudaSuccess ? 0 : 3;
+}

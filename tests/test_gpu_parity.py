@@ -256,3 +256,57 @@ def test_errors_are_reported_not_fatal(built):
     with pytest.raises(m.McmcError):
         ctx.get_samples(5)
     ctx.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("prec", [0, 1])
+def test_checkpoint_resume_is_bit_identical(built, prec, tmp_path):
+    """12 iterations in one go == 5 iterations, checkpoint, new context, restore, 7 more (3 windows,
+    adaptive preset so that the step size and the counters matter)."""
+    m, O = built
+    rows, W = 3000, 3
+    cfg = m.reference_config(precision=prec, leapfrog_steps=5, burn_in=4, adapt_steps=4, sample_capacity=8,
+                             trace_iters=12, eps0=0.02, seed=77)
+
+    def make():
+        ctx = m.Context(cfg, n_windows=W, rows=rows)
+        for w in range(W):
+            x, y, _ = m.synth_window(5, w, rows)
+            ctx.set_window_data(w, x * np.float32(0.05), y, global_window=10 + w)
+        return ctx
+
+    a = make()
+    a.run_chain(12)
+    b = make()
+    b.run_chain(5)
+    path = str(tmp_path / "chain.ckpt")
+    b.save_checkpoint(path)
+    b.close()
+    c = make()
+    c.load_checkpoint(path)
+    c.run_chain(7)
+    for w in range(W):
+        assert a.chain_info(w) == c.chain_info(w)
+        sa, sc = a.get_state(w), c.get_state(w)
+        assert np.array_equal(sa["w"], sc["w"]) and np.array_equal(sa["grad"], sc["grad"])
+        assert sa["loglik"] == sc["loglik"]
+        assert np.array_equal(a.get_samples(w), c.get_samples(w))
+        ta, tc = a.get_trace(w), c.get_trace(w)
+        assert np.array_equal(ta["accepted"], tc["accepted"]) and np.array_equal(ta["log_acpt"], tc["log_acpt"])
+    # a checkpoint of another configuration is refused
+    other = m.Context(m.reference_config(precision=prec, leapfrog_steps=6, burn_in=4, adapt_steps=4,
+                                         sample_capacity=8, trace_iters=12, eps0=0.02, seed=77),
+                      n_windows=W, rows=rows)
+    for w in range(W):
+        x, y, _ = m.synth_window(5, w, rows)
+        other.set_window_data(w, x, y, global_window=10 + w)
+    with pytest.raises(m.McmcError):
+        other.load_checkpoint(path)
+    # export: raw samples + JSON side file
+    prefix = str(tmp_path / "out")
+    c.export_samples(prefix)
+    raw = np.fromfile(prefix + ".samples.f32", np.float32).reshape(W, 8, c.P)
+    assert np.array_equal(raw[1], c.get_samples(1))
+    import json
+    meta = json.load(open(prefix + ".json"))
+    assert meta["shape"] == [W, 8, c.P] and len(meta["trace"]) == W and meta["windows"][0]["iterations"] == 12
