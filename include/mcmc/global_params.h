@@ -23,3 +23,6 @@ static constexpr int FEAT_DIM[] = {22, 40, 1};
 static constexpr int NUM_PARAMS = FEAT_DIM[0] * FEAT_DIM[1] + FEAT_DIM[1] + FEAT_DIM[1] * FEAT_DIM[2] + FEAT_DIM[2];
 static constexpr int N_SAMPLES = 58368;
 static constexpr int N_COLS = FEAT_DIM[0];
+static constexpr int TOTAL_COLS = 149;
+static constexpr int SKIP_COLS = 2;
+static constexpr const char* DATA_FNAME = "returns_and_features_for_mcmc.txt";

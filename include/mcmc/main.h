@@ -13,8 +13,10 @@
 //     variant leaves them with (L-1 rotations, mcmc_step_ffma.h:382-393) in both
 //     precisions, so the TC-only replay of main.h:224-227 must not be done;
 //     grad_prev's contents after the call are unspecified;
-//   * main_loop generates a synthetic window (the reference's data file is not
-//     distributed) and runs the whole chain on the device.
+//   * main_loop reads DATA_FNAME in the reference's text layout when that file
+//     is present (mcmc_b200_read_table) and otherwise generates a synthetic
+//     window (the reference's data file is not distributed); either way the
+//     whole chain runs on the device.
 #pragma once
 #include <chrono>
 #include <cstdio>
@@ -139,9 +141,19 @@ void main_loop() {
   mcmc_b200_ctx* ctx = nullptr;
   check(mcmc_b200_create(&cfg, dev, 1, N_SAMPLES, &ctx), "mcmc_b200_create");
   std::vector<float> x((size_t)N_SAMPLES * N_COLS), y(N_SAMPLES);
-  check(mcmc_b200_synth_window(SEED_INIT, 0, N_SAMPLES, N_COLS, FEAT_DIM[1], x.data(), y.data(), nullptr),
-        "mcmc_b200_synth_window");
-  for (auto& v : x) v *= 0.001f;  // main.h:162-164 scales the features
+  // main.h:158-164: read the dataset, scale the features by 0.001
+  if (FILE* probe = std::fopen(DATA_FNAME, "r")) {
+    std::fclose(probe);
+    std::printf("Reading dataset...\n");
+    check(mcmc_b200_read_table(DATA_FNAME, N_SAMPLES, TOTAL_COLS, SKIP_COLS, N_COLS, 0.001f, x.data(), y.data()),
+          "mcmc_b200_read_table");
+    std::printf("Dataset read successfully\n");
+  } else {
+    std::printf("'%s' not found: using a synthetic window of the same shape\n", DATA_FNAME);
+    check(mcmc_b200_synth_window(SEED_INIT, 0, N_SAMPLES, N_COLS, FEAT_DIM[1], x.data(), y.data(), nullptr),
+          "mcmc_b200_synth_window");
+    for (auto& v : x) v *= 0.001f;
+  }
   check(mcmc_b200_set_window_data(ctx, 0, 0, x.data(), y.data(), 0), "mcmc_b200_set_window_data");
   const auto t0 = std::chrono::high_resolution_clock::now();
   check(mcmc_b200_run_chain(ctx, BURN_IN_STEPS + SAMPLE_STEPS), "mcmc_b200_run_chain");

@@ -177,6 +177,20 @@ int mcmc_b200_final_loss(mcmc_b200_ctx* ctx, int window, int first, int count, d
                          double* mean_logprior);
 
 /*
+ * Dataset text reader: the layout the reference's read_data scans
+ * (io.h:42-80, sizes in global_params.h:61-65 there).  Whitespace-separated
+ * tokens: total_cols header tokens (ignored), then `rows` rows of total_cols
+ * tokens, of which the first skip_cols are ignored, the next one is the label,
+ * the next D are the features and the rest is ignored.  Features are
+ * multiplied by feature_scale (the reference scales by 0.001 in a separate
+ * device pass, main.h:162-164).  x_out [rows][D] and y_out [rows] are host
+ * arrays.  Host-only: needs no GPU.  The reference aborts on a missing file;
+ * this returns MCMC_B200_ERR_INVALID with the reason in last_error.
+ */
+int mcmc_b200_read_table(const char* path, int64_t rows, int total_cols, int skip_cols, int D,
+                         float feature_scale, float* x_out, float* y_out);
+
+/*
  * Checkpoint / resume.  The reference keeps samples and chain state in device
  * memory only and loses them when the process ends (main.h:183,277-283,295).
  * A checkpoint is one host blob: a fixed header (configuration fingerprint,

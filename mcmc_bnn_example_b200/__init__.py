@@ -21,7 +21,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libmcmc_b200.so")
-_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "synth.cu", "noalloc.cu"]
+_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "synth.cu", "noalloc.cu", "io.cu"]
 _HEADERS = ["common.cuh", "chain.cuh", "philox.h"]
 
 OK = 0
@@ -39,6 +39,7 @@ EXPORTS = [
     "mcmc_b200_log_acpt", "mcmc_b200_synth_window", "mcmc_b200_philox_normal", "mcmc_b200_philox_raw",
     "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
     "mcmc_b200_checkpoint_size", "mcmc_b200_checkpoint_save", "mcmc_b200_checkpoint_load",
+    "mcmc_b200_read_table",
 ]
 
 
@@ -157,6 +158,16 @@ def potential_and_grad_static(cfg, x_ptr, y_ptr, rows, w_ptr, grad_ptr, scalars_
     _check(lib().mcmc_b200_potential_and_grad_static(C.byref(cfg), _vp(x_ptr), _vp(y_ptr), C.c_int64(rows),
                                                      _vp(w_ptr), _vp(grad_ptr), _vp(scalars_ptr),
                                                      _vp(stream)))
+
+
+def read_table(path, rows, total_cols=149, skip_cols=2, D=22, feature_scale=0.001):
+    """The reference's dataset text layout (io.h:42-80 there): header of total_cols tokens, then per row
+    skip_cols ignored, one label, D features, the rest ignored.  Returns (x [rows][D] scaled, y [rows])."""
+    x = np.empty((rows, D), np.float32)
+    y = np.empty(rows, np.float32)
+    _check(lib().mcmc_b200_read_table(os.fsencode(path), C.c_int64(rows), total_cols, skip_cols, D,
+                                      C.c_float(feature_scale), _fp(x), _fp(y)))
+    return x, y
 
 
 def nccl_unique_id():

@@ -295,12 +295,21 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
     if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
   } else {
     const long long capacity = (long long)c->num_sms * c->ctas_per_sm;
-    long long s = cfg->slices > 0 ? cfg->slices : capacity / n_windows;
+    // the fewest CTAs per window that keep the longest CTA as short as `cap` CTAs would: fewer partial
+    // vectors to sum and fewer per-CTA prologues for the same critical path
+    auto balanced = [&](long long cap) {
+      if (cap < 1) cap = 1;
+      if (cap > n_tiles) cap = n_tiles;
+      if (cap > MAX_SLICES) cap = MAX_SLICES;
+      const long long tiles_per_cta = (n_tiles + cap - 1) / cap;
+      return (n_tiles + tiles_per_cta - 1) / tiles_per_cta;
+    };
+    long long s = cfg->slices > 0 ? cfg->slices : balanced(capacity / n_windows);
     if (s < 1) s = 1;
     if (s > n_tiles) s = n_tiles;
     if (s > MAX_SLICES) s = MAX_SLICES;
     c->slices = (int)s;
-    long long sx = cfg->slices > 0 ? cfg->slices : capacity;
+    long long sx = cfg->slices > 0 ? cfg->slices : balanced(capacity);
     if (sx > n_tiles) sx = n_tiles;
     if (sx > MAX_SLICES) sx = MAX_SLICES;
     if (sx < 1) sx = 1;

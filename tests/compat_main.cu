@@ -5,12 +5,19 @@
 #include <cstdlib>
 #include <vector>
 
+#include "mcmc/io.h"
 #include "mcmc/main.h"
 
 int main(int argc, char** argv) {
   using namespace mcmc;
   if (argc > 1 && std::string(argv[1]) == "main_loop") {
     main_loop<float>();
+    return 0;
+  }
+  if (argc > 2 && std::string(argv[1]) == "read_data") {  // the reference's reader signature (io.h:42-43)
+    DeviceMatrix<float> data(N_SAMPLES, N_COLS), labels(N_SAMPLES, FEAT_DIM[NUM_LAYERS]);
+    read_data(data, labels, argv[2]);
+    std::printf("read %zu x %zu\n", data.rows(), data.cols());
     return 0;
   }
   cudaStream_t stream = cudaStreamPerThread;

@@ -87,3 +87,32 @@ def test_synthetic_window_is_deterministic_and_teacher_consistent(built):
     pred = O.predict_mean(O.baseline_model(), x, t[None, :])
     resid = y - pred
     assert abs(resid.std() - 0.05) < 0.005 and abs(resid.mean()) < 0.005
+
+
+def test_read_table_matches_a_plain_parse(tmp_path):
+    """The reference's dataset layout (io.h:42-80 there): 149 header tokens, rows of 149 tokens =
+    2 ignored + label + 22 features + rest ignored.  Host-only: runs without a GPU."""
+    import mcmc_bnn_example_b200 as m
+    m.build()
+    rng = np.random.default_rng(3)
+    rows, total, skip, D = 37, 149, 2, 22
+    table = rng.standard_normal((rows, total)) * 10.0
+    path = tmp_path / "returns_and_features_for_mcmc.txt"
+    with open(path, "w") as f:
+        f.write(" ".join("col%d" % j for j in range(total)) + "\n")
+        for i in range(rows):
+            toks = ["%.9g" % v for v in table[i]]
+            toks[0] = "2019-01-%02d" % (i % 28 + 1)      # the skipped columns need not be numbers
+            toks[1] = "TICK%d" % i
+            f.write(("\t" if i % 2 else " ").join(toks) + "\n")
+    x, y = m.read_table(str(path), rows)
+    want_y = table[:, skip].astype(np.float32)
+    want_x = (table[:, skip + 1:skip + 1 + D].astype(np.float32) * np.float32(0.001)).astype(np.float32)
+    # the file holds 9 significant digits: the parse may differ from the float32 of the double by one ulp
+    assert np.allclose(y, want_y, rtol=2e-7, atol=0)
+    assert np.allclose(x, want_x, rtol=3e-7, atol=0)
+    # fewer rows than asked for, and a missing file, are errors with a message (the reference aborts)
+    with pytest.raises(m.McmcError, match="row 37"):
+        m.read_table(str(path), rows + 1)
+    with pytest.raises(m.McmcError, match="cannot open"):
+        m.read_table(str(tmp_path / "nope.txt"), 1)

@@ -15,7 +15,7 @@ EXE = os.path.join(ROOT, "tests", "_build", "compat_main")
 def _build(m):
     src = os.path.join(ROOT, "tests", "compat_main.cu")
     deps = [src, m.LIB_PATH] + [os.path.join(ROOT, "include", "mcmc", f) for f in
-                                ("main.h", "utils_matrix.h", "global_params.h")]
+                                ("main.h", "utils_matrix.h", "global_params.h", "io.h")]
     if os.path.exists(EXE) and all(os.path.getmtime(EXE) >= os.path.getmtime(d) for d in deps):
         return
     os.makedirs(os.path.dirname(EXE), exist_ok=True)
