@@ -27,6 +27,8 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
   const int win = blockIdx.x;
   const int tid = threadIdx.x;
   const size_t o = (size_t)win * a.Pp;
+  pdl_trigger();
+  pdl_wait();
   const int iter = (a.mode == ACC_ITERATE) ? a.iter[win] : 0;
   const float eps = a.eps ? a.eps[win] : 0.f;
   const uint32_t gwin = a.gwin ? (uint32_t)a.gwin[win] : 0u;
@@ -140,8 +142,7 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
 }
 
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st) {
-  hmc_accept_kernel<<<windows, ACC_THREADS, 0, st>>>(a);
-  return cudaGetLastError();
+  return launch_chain_kernel(hmc_accept_kernel, dim3(windows), dim3(ACC_THREADS), 0, st, a);
 }
 
 // ---- dataset repack ------------------------------------------------------
@@ -175,7 +176,7 @@ cudaError_t launch_repack(const float* x, const float* y, float* out, long long 
 // Used (a) when many CTAs touch one window (few windows per GPU): one small launch sums the
 // slots once instead of every CTA of the next launch summing all of them in its prologue, and
 // (b) for row sharding, where the result is what is all-reduced.  Fixed order: deterministic.
-constexpr int RED_PARAMS = 32, RED_GROUPS = 8;
+constexpr int RED_PARAMS = 32, RED_GROUPS = 32;  // every load of a thread is in flight at once
 __global__ void __launch_bounds__(RED_PARAMS* RED_GROUPS)
 reduce_partials_kernel(const float* __restrict__ partial, const double* __restrict__ ll_partial, int slices,
                        const int* __restrict__ nslot, int P, int Pp, double* __restrict__ red) {
@@ -186,9 +187,12 @@ reduce_partials_kernel(const float* __restrict__ partial, const double* __restri
   const int pi = threadIdx.x % RED_PARAMS, gi = threadIdx.x / RED_PARAMS;
   const int p = blockIdx.x * RED_PARAMS + pi;
   double* r = red + (size_t)win * (Pp + 4);
+  pdl_trigger();
+  pdl_wait();
   float g = 0.f;
   if (p < P) {
     const float* src = partial + (size_t)win * slices * Pp + p;
+#pragma unroll 8
     for (int s = gi; s < ns; s += RED_GROUPS) g += src[(size_t)s * Pp];
   }
   sg[gi][pi] = g;
@@ -221,9 +225,8 @@ cudaError_t launch_reduce_partials(const float* partial, const double* ll_partia
                                    const int* nslot, int P, int Pp, double* red, int windows,
                                    cudaStream_t st) {
   dim3 grid((Pp + RED_PARAMS - 1) / RED_PARAMS, windows);
-  reduce_partials_kernel<<<grid, RED_PARAMS * RED_GROUPS, 0, st>>>(partial, ll_partial, slices, nslot, P, Pp,
-                                                                  red);
-  return cudaGetLastError();
+  return launch_chain_kernel(reduce_partials_kernel, grid, dim3(RED_PARAMS * RED_GROUPS), 0, st, partial,
+                             ll_partial, slices, nslot, P, Pp, red);
 }
 
 // ---- posterior-mean prediction -------------------------------------------

@@ -4,6 +4,8 @@
 #pragma once
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 namespace mcmc_b200 {
 
@@ -216,6 +218,41 @@ __device__ __forceinline__ double block_sum_f64(double v, double* scratch /* >= 
   const int nw = (blockDim.x + 31) >> 5;
   for (int i = 0; i < nw; ++i) t += scratch[i];
   return t;
+}
+
+// ---- programmatic dependent launch -----------------------------------------
+// The chain is a string of short dependent launches (gradient, partial sum, accept).  A kernel
+// launched with the programmatic-serialization attribute may start while its predecessor is still
+// draining: its CTAs are scheduled as the predecessor's CTAs exit, do their private set-up (barriers,
+// tensor-memory allocation, first row tiles — nothing the predecessor writes) and then block in
+// pdl_wait() until the predecessor has completed and its writes are visible.  Every kernel of the
+// chain calls pdl_trigger() (lets ITS successor start early) and pdl_wait() before it touches
+// anything a predecessor produced, and writes global memory only after the wait.  Without the launch
+// attribute both calls do nothing.  MCMC_B200_NO_PDL=1 turns the attribute off.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("MCMC_B200_NO_PDL");
+    return !(e && e[0] == '1');
+  }();
+  return on;
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chain_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
 }  // namespace mcmc_b200

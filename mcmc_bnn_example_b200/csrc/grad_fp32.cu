@@ -110,10 +110,12 @@ __global__ void __launch_bounds__(NT, MINB) grad_fp32_kernel(const GradParams g)
     mbar_fence_init();
   }
   __syncthreads();
-  if (tid == 0 && t0 < t1) {
+  if (tid == 0 && t0 < t1) {  // the dataset is not written by any kernel of the chain
     mbar_expect_tx(&bars[0], TILE_BYTES);
     bulk_g2s(xs, xw + (size_t)t0 * TILE * KP, TILE_BYTES, &bars[0]);
   }
+  pdl_trigger();
+  pdl_wait();
   // fused leapfrog update; parameters land in the layout the lanes read
   for (int p = tid; p < G::P; p += NT) {
     const float w = leapfrog_param(g, win, p, slice == 0);
@@ -316,8 +318,8 @@ static cudaError_t launch_fp32_t(const GradParams& g, int slices, int windows, c
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  grad_fp32_kernel<H, HPL, NT, MINB><<<dim3(slices, windows), NT, G::SMEM, st>>>(g);
-  return cudaGetLastError();
+  return launch_chain_kernel(grad_fp32_kernel<H, HPL, NT, MINB>, dim3(slices, windows), dim3(NT), G::SMEM, st,
+                             g);
 }
 
 int fp32_tile_rows(int H) { (void)H; return FP32_TILE; }

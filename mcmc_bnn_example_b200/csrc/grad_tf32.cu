@@ -301,8 +301,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   const uint32_t tmem = tmem_slot;
   const uint32_t tmem_g = tmem + G::G_COL0;
   const uint32_t w0s_addr = smem_u32(w0s);
-  const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];
+  const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];  // host-written table
   bool ok = true;
+  // everything above is private set-up; from here on the kernel reads what its predecessor wrote
+  pdl_trigger();
+  pdl_wait();
 
   // Every segment has three CTA-wide barriers, executed by both roles:
   //   S1 parameters staged   S2 all tiles of the segment done   S3 read-out done
@@ -650,9 +653,8 @@ static cudaError_t launch_tf32_t(const void* tmap_mn, const GradParams& g, int c
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  grad_tf32_kernel<H><<<ctas, TF32_THREADS, G::SMEM, st>>>(*reinterpret_cast<const CUtensorMap*>(tmap_mn), g,
-                                                           dbg);
-  return cudaGetLastError();
+  return launch_chain_kernel(grad_tf32_kernel<H>, dim3(ctas), dim3(TF32_THREADS), G::SMEM, st,
+                             *reinterpret_cast<const CUtensorMap*>(tmap_mn), g, dbg);
 }
 
 cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
