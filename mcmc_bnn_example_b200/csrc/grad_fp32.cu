@@ -140,11 +140,13 @@ __global__ void __launch_bounds__(NT, MINB) grad_fp32_kernel(const GradParams g)
   for (int j = 0; j < HPL; ++j) w1r[j] = w1s[cg * HPL + j];
   const float b1 = b1s;
 
-  float acc[KPT][HPL];  // dW0 rows kh*12 .. kh*12+11 (row 22 = db0 through the constant-1 column)
+  // dW0 rows kh*12 .. kh*12+11 (row 22 = db0 through the constant-1 column), two features per register
+  // pair: the backward FMAs are issued as packed f32x2 (half the issue slots)
+  uint64_t acc2[KPT / 2][HPL];
 #pragma unroll
-  for (int k = 0; k < KPT; ++k)
+  for (int k = 0; k < KPT / 2; ++k)
 #pragma unroll
-    for (int j = 0; j < HPL; ++j) acc[k][j] = 0.f;
+    for (int j = 0; j < HPL; ++j) acc2[k][j] = 0ull;
   float dw1[HPL];
 #pragma unroll
   for (int j = 0; j < HPL; ++j) dw1[j] = 0.f;
@@ -230,18 +232,21 @@ __global__ void __launch_bounds__(NT, MINB) grad_fp32_kernel(const GradParams g)
     for (int s = 0; s < RPS; ++s) {
       const int row = s * RSUB + rsub;
       const float* xr = xt + row * KP + kh * KPT;
-      float xk[KPT];
+      uint64_t xk2[KPT / 2];
 #pragma unroll
       for (int q = 0; q < KPT / 4; ++q) {
         const float4 v = *reinterpret_cast<const float4*>(xr + 4 * q);
-        xk[4 * q] = v.x; xk[4 * q + 1] = v.y; xk[4 * q + 2] = v.z; xk[4 * q + 3] = v.w;
+        xk2[2 * q] = pack2(v.x, v.y);
+        xk2[2 * q + 1] = pack2(v.z, v.w);
       }
       float ev[HPL];
       load_units<H, HPL, NT>(es + row * H, cg, ev);
 #pragma unroll
-      for (int k = 0; k < KPT; ++k)
+      for (int j = 0; j < HPL; ++j) {
+        const uint64_t e2 = pack2(ev[j], ev[j]);
 #pragma unroll
-        for (int j = 0; j < HPL; ++j) acc[k][j] = fmaf(xk[k], ev[j], acc[k][j]);
+        for (int k = 0; k < KPT / 2; ++k) acc2[k][j] = fma2(xk2[k], e2, acc2[k][j]);
+      }
     }
     __syncthreads();
   }
@@ -254,7 +259,11 @@ __global__ void __launch_bounds__(NT, MINB) grad_fp32_kernel(const GradParams g)
       const int kk = kh * KPT + k;
       if (kk <= D) {  // feature 23 is y: not a gradient row
 #pragma unroll
-        for (int j = 0; j < HPL; ++j) r[kk * H + cg * HPL + j] = acc[k][j];
+        for (int j = 0; j < HPL; ++j) {
+          float lo, hi;
+          unpack2(acc2[k / 2][j], lo, hi);
+          r[kk * H + cg * HPL + j] = (k & 1) ? hi : lo;
+        }
       }
     }
   }
