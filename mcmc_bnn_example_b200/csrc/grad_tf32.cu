@@ -170,6 +170,11 @@ __device__ __forceinline__ uint64_t umma_desc_k128(uint32_t smem_addr) {
 __device__ __forceinline__ uint64_t umma_desc_mn32(uint32_t smem_addr, uint32_t atom_stride) {
   return umma_desc(smem_addr, atom_stride, 512, 1);
 }
+// Moves a descriptor's start address by `units` x 16 bytes (the address field is the low 14 bits; the
+// operands here never carry out of it): one 32-bit add instead of rebuilding the descriptor per MMA.
+__device__ __forceinline__ uint64_t umma_desc_advance(uint64_t d, uint32_t units) {
+  return (d & 0xFFFFFFFF00000000ull) | (uint64_t)((uint32_t)d + units);
+}
 // Instruction descriptor: F32 accumulate, TF32 x TF32, dense.
 __host__ __device__ constexpr uint32_t umma_idesc_tf32(int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) |
@@ -306,7 +311,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
         const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE;
         const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
-        const uint32_t ea = smem_u32(es + wg * G::ES_WG_BYTES);
+        // descriptors of K block 0 / row stage 0; the others differ only in the start address
+        const uint64_t wdesc0 = umma_desc_k128(w0s_addr);
+        const uint64_t adesc0 = umma_desc_k128(smem_u32(es + wg * G::ES_WG_BYTES));
+        const uint64_t bdesc0 = umma_desc_mn32(smem_u32(xb + wg * NST * G::TILE_BYTES), G::TILE_BYTES);
+        uint32_t stage = c_issued % NST;  // row stage of tile n, kept as a running counter
         auto issue_fwd = [&](uint32_t n) {
           named_sync(BAR_ROWS0 + wg, 160);
           if (lane == 0) {
@@ -315,7 +324,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
             if (!ABL(32))
 #pragma unroll
             for (int kb = 0; kb < 3; ++kb)
-              tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_k128(w0s_addr + kb * 32), IDESC_FWD, kb > 0);
+              tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_advance(wdesc0, kb * 2), IDESC_FWD, kb > 0);
             tc_commit(&bar_fwd[wg]);
           }
           __syncwarp();
@@ -327,23 +336,24 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           named_sync(BAR_E0 + wg, 160);
           if (lane == 0) {
             tc_fence_after();
-            const uint32_t xa = smem_u32(xb + (wg * NST + n % NST) * G::TILE_BYTES);
+            const uint64_t bd = umma_desc_advance(bdesc0, stage * (G::TILE_BYTES >> 4));
             if (!ABL(1))
 #pragma unroll
             for (int kb = 0; kb < TF32_TILE / 8; ++kb)
-              tc_mma_tf32_ss(g_t, umma_desc_k128(ea + (kb >> 2) * G::ES_ATOM_BYTES + (kb & 3) * 32),
-                             umma_desc_mn32(xa + kb * 1024, G::TILE_BYTES), IDESC_BWD,
-                             (i == 0 && kb == 0) ? 0u : 1u);
+              tc_mma_tf32_ss(g_t,
+                             umma_desc_advance(adesc0, (kb >> 2) * (G::ES_ATOM_BYTES >> 4) + (kb & 3) * 2),
+                             umma_desc_advance(bd, kb * 64), IDESC_BWD, (i == 0 && kb == 0) ? 0u : 1u);
             tc_commit(&bar_bwd[wg]);
             if (i + NST < cnt && !ABL(256)) {
               ok = ok && mbar_wait(&bar_bwd[wg], n & 1, g.status, 213);
               if (ok) {
-                mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
-                tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
-                            grow0 + (t0 + wg + (i + NST) * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+                mbar_expect_tx(&bar_tma[wg][stage], G::TILE_BYTES);
+                tma_load_2d(xb + (wg * NST + stage) * G::TILE_BYTES, &tmap_mn, 0,
+                            grow0 + (t0 + wg + (i + NST) * NWG) * TF32_TILE, &bar_tma[wg][stage]);
               }
             }
           }
+          stage = stage + 1 == NST ? 0 : stage + 1;
           __syncwarp();
         }
         c_issued += cnt;
@@ -355,6 +365,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     // =====================  compute warpgroups: one row per thread  =====================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TF32_COMPUTE_REGS));
     uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
+    uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
     const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
     const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
     const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE + lane_off;
@@ -414,9 +425,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       double llacc = 0.0;
 
       // hands this thread's row of the landed tile to the tensor core (forward A operand); returns y
-      auto stage_row = [&](uint32_t n) -> float {
-        const int stage = n % NST;
-        if (!ABL(256)) ok = ok && mbar_wait(&bar_tma[wg][stage], (n / NST) & 1, g.status, 201);
+      auto stage_row = [&]() -> float {
+        const uint32_t stage = st_stage, phase = st_phase;  // of the tile being staged
+        st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
+        st_phase ^= (st_stage == 0) ? 1u : 0u;
+        if (!ABL(256)) ok = ok && mbar_wait(&bar_tma[wg][stage], phase, g.status, 201);
         // 32-byte chunk j of a row sits at position j ^ (row % 4)
         const unsigned char* xrow = xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128;
         float4 xr[6];
@@ -449,7 +462,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       PROF_DECL
       float y = 0.f;
       if (my_nt > 0) {
-        y = stage_row(n_done);
+        y = stage_row();
         publish_row();
       }
       PROF_MARK(9)
@@ -462,7 +475,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         // forward(n) is done with the A operand: the next tile's rows go in now, so that forward(n+1)
         // (into the other accumulator buffer) has this whole tile's epilogue to complete
         float y_next = 0.f;
-        if (i + 1 < my_nt) y_next = stage_row(n + 1);
+        if (i + 1 < my_nt) y_next = stage_row();
         PROF_MARK(1)
         const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
         float z[H];
