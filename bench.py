@@ -301,6 +301,7 @@ def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
 
 
 def main():
+    global ROWS, P
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
@@ -311,6 +312,8 @@ def main():
     ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme"],
                     help="windows: configs[2], windows sharded over GPUs (the headline); rows: configs[1], ONE "
                          "window whose rows are sharded, one NCCL all-reduce per leapfrog step")
+    ap.add_argument("--rows", type=int, default=ROWS, help="rows per window (configs[4]: 1048576)")
+    ap.add_argument("--hidden", type=int, default=40, help="hidden units (configs[4]: 128)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -349,12 +352,19 @@ def main():
     prec = m.PREC_TF32 if args.precision == "tf32" else m.PREC_FP32
     K, W = args.steps, args.warmup
 
-    # synthetic dataset in pinned host memory (also the source of the e2e uploads)
-    xh = torch.empty((n_local, ROWS, D), dtype=torch.float32, pin_memory=True)
-    yh = torch.empty((n_local, ROWS), dtype=torch.float32, pin_memory=True)
+    custom = (args.rows != ROWS) or (args.hidden != 40)
+    ROWS, HID = args.rows, args.hidden
+    P = D * HID + 2 * HID + 1
+
+    # synthetic dataset in pinned host memory (also the source of the e2e uploads).  Generating a window
+    # costs rows x D x H host multiply-adds: for the large custom shapes only the first few windows of a
+    # rank are generated and the rest repeat them (the kernels' work does not depend on the values).
+    n_distinct = n_local if not custom else min(n_local, 2)
+    xh = torch.empty((n_distinct, ROWS, D), dtype=torch.float32, pin_memory=True)
+    yh = torch.empty((n_distinct, ROWS), dtype=torch.float32, pin_memory=True)
     xn, yn = xh.numpy(), yh.numpy()
-    for i in range(n_local):
-        xi, yi, _ = m.synth_window(SEED, w0 + i, ROWS)
+    for i in range(n_distinct):
+        xi, yi, _ = m.synth_window(SEED, w0 + i, ROWS, D, HID)
         xn[i], yn[i] = xi, yi
 
     def barrier():
@@ -363,13 +373,13 @@ def main():
 
     def make_ctx(sample_capacity):
         cfg = m.baseline_config(precision=prec, seed=SEED, sample_capacity=sample_capacity,
-                                leapfrog_steps=LEAPFROG, eps0=EPS)
+                                leapfrog_steps=LEAPFROG, eps0=EPS, H=HID)
         return m.Context(cfg, n_windows=n_local, rows=ROWS, device=local_rank)
 
     def upload(ctx):
         for i in range(n_local):
-            ctx.set_window_data_ptr(i, xh[i].data_ptr(), yh[i].data_ptr(), is_device=False,
-                                    global_window=w0 + i)
+            ctx.set_window_data_ptr(i, xh[i % n_distinct].data_ptr(), yh[i % n_distinct].data_ptr(),
+                                    is_device=False, global_window=w0 + i)
 
     # ---------------- device-resident measurement ----------------
     ctx = make_ctx(0)
@@ -448,9 +458,14 @@ def main():
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": args.precision, "data": "synthetic",
         "config": {
-            "workload": "BASELINE configs[2]: 200 windows x 58368 rows x 22 features FP32, 22-40-1 MLP "
-                        "(961 params), Gaussian sigma=1, N(0,1) prior, L=10, eps=1e-3, windows sharded "
-                        "200/N with no communication",
+            "workload": ("BASELINE configs[2]: 200 windows x 58368 rows x 22 features FP32, 22-40-1 MLP "
+                         "(961 params), Gaussian sigma=1, N(0,1) prior, L=10, eps=1e-3, windows sharded "
+                         "200/N with no communication") if not custom else
+                        ("%s: %d windows x %d rows x 22 features, 22-%d-1 MLP (%d params), Gaussian sigma=1, "
+                         "N(0,1) prior, L=10, eps=1e-3, windows sharded over GPUs; %d distinct synthetic "
+                         "windows per rank, repeated"
+                         % ("BASELINE configs[4]" if (args.windows, ROWS, HID) == (64, 1048576, 128)
+                            else "custom shape", args.windows, ROWS, HID, P, n_distinct)),
             "windows": args.windows, "windows_per_gpu": n_local, "rows": ROWS, "leapfrog_steps": LEAPFROG,
             "gradients_per_sec": value * LEAPFROG,
             "l2": "inputs larger than L2 between timed iterations (%.0f MB per GPU vs 126 MB L2)"

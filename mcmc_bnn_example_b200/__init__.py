@@ -21,8 +21,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libmcmc_b200.so")
-_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "synth.cu", "noalloc.cu", "io.cu"]
-_HEADERS = ["common.cuh", "chain.cuh", "philox.h"]
+_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "grad_tf32_wide.cu", "synth.cu", "noalloc.cu", "io.cu"]
+_HEADERS = ["common.cuh", "chain.cuh", "philox.h", "tc05.cuh"]
 
 OK = 0
 LIK_STUDENT_T, LIK_GAUSSIAN = 0, 1

@@ -74,6 +74,7 @@ int fp32_tile_rows(int H);
 cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
                              cudaStream_t st);
 int tf32_supported(int H);
+cudaError_t launch_grad_tf32_wide(const void* tmap_mn, const GradParams& g, int ctas, cudaStream_t st);
 constexpr int TF32_TILE = 128;
 
 }  // namespace mcmc_b200

@@ -65,18 +65,54 @@ def test_tf32_and_fp32_modes_agree_with_exact_oracle(built, prec):
     ctx.close()
 
 
-def test_fp32_wide_model(built):
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("rows", [100, 3000, 40000])
+def test_wide_model(built, prec, rows):
+    """22-128-1 (3073 parameters, the scaled stress configuration) in both precisions."""
     m, O = built
-    rows, Hw = 3000, 128
+    Hw = 128
     Pw = 22 * Hw + 2 * Hw + 1
     x, y, _ = m.synth_window(3, 0, rows, H=Hw)
     w = _w(5, 0.1, Pw)
-    ctx = m.Context(m.baseline_config(H=Hw), n_windows=1, rows=rows)
+    ctx = m.Context(m.baseline_config(H=Hw, precision=prec), n_windows=1, rows=rows)
     ctx.set_window_data(0, x, y)
-    got = ctx.potential_and_grad(0, w)
-    ref = O.logp_grad(O.baseline_model(H=Hw), x, y, w)
-    assert _grad_err(got["grad"], ref["grad"]) < 1e-5
-    assert abs(got["loglik"] - ref["loglik"]) <= 1e-5 * abs(ref["loglik"])
+    got = ctx.potential_and_grad(0, w, want_row_loss=True)
+    ref = O.logp_grad(O.baseline_model(tf32=bool(prec), H=Hw), x, y, w, want_losses=True)
+    tol = TOL[prec]
+    assert _grad_err(got["grad"], ref["grad"]) < tol
+    assert abs(got["loglik"] - ref["loglik"]) <= tol * abs(ref["loglik"])
+    assert np.allclose(got["row_loss"], ref["row_loss"], rtol=tol * 10, atol=tol)
+    ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_wide_model_chain_matches_oracle(built, prec):
+    """A short multi-window chain at 128 hidden units: device draws replayed through the oracle."""
+    m, O = built
+    Hw, rows, W, iters = 128, 6000, 3, 6
+    Pw = 22 * Hw + 2 * Hw + 1
+    cfg = m.baseline_config(H=Hw, precision=prec, leapfrog_steps=4, eps0=2e-4, sample_capacity=iters,
+                            trace_iters=iters, seed=9)
+    ctx = m.Context(cfg, n_windows=W, rows=rows)
+    data = []
+    for w in range(W):
+        x, y, _ = m.synth_window(8, w, rows, H=Hw)
+        ctx.set_window_data(w, x, y, global_window=w)
+        data.append((x, y))
+    ctx.run_chain(iters)
+    model = O.baseline_model(tf32=bool(prec), H=Hw)
+    sampler = O.baseline_sampler(L=4, eps=2e-4)
+    for w in range(W):
+        tr = ctx.get_trace(w)
+        ref = O.hmc_chain(model, sampler, data[w][0], data[w][1], tr["momenta"], tr["log_u"])
+        # decisions must agree wherever the draw is not within the kernel tolerance of the ratio
+        clear = np.abs(ref["log_acpt"] - tr["log_u"]) > 0.05
+        assert np.array_equal(ref["accepted"][clear], tr["accepted"][clear])
+        if np.array_equal(ref["accepted"], tr["accepted"]):
+            got = ctx.get_samples(w)
+            tol = TOL[prec]
+            assert np.abs(got - ref["samples"]).max() <= tol * max(1e-3, np.abs(ref["samples"]).max())
+            assert np.allclose(tr["log_acpt"], ref["log_acpt"], rtol=1e-2, atol=5e-2)
     ctx.close()
 
 
