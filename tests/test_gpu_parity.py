@@ -194,7 +194,7 @@ def test_posterior_mean_prediction_over_800_samples(built, prec):
     # FP32: the stated 1 %.  TF32: the device chain and the CPU replay take a different accept
     # decision somewhere in 800 iterations and decorrelate from there; the oracle's own exact and
     # TF32 modes differ by 1.1 - 1.5 % on this case for the same reason, so the bound for the
-    # tensor-core mode is the chain-divergence level, not a kernel error (see DESIGN.md section 4).
+    # tensor-core mode is the chain-divergence level, not a kernel error.
     assert rel_l2 < (1e-2 if prec == 0 else 2.5e-2)
     agree = np.mean(tr["accepted"] == ref["accepted"])
     assert agree == 1.0 if prec == 0 else agree > 0.97

@@ -3,8 +3,8 @@ kernel, built unmodified from the reference's headers (oracle/ref_harness.cu)
 and run here on the GPU, at the shapes the reference fixes at compile time
 (58368 rows, 22 -> 40 -> 1, Student-t(100, 2.2), N(0, 200^2) prior).
 
-Also writes the captured reference outputs to gpurun_out/golden/ so that they
-can be committed under tests/golden/ for the CPU-only suite."""
+Also writes the captured reference outputs into the run's output folder so that
+they can be committed under tests/golden/ for the CPU-only suite."""
 import ctypes as C
 import os
 
