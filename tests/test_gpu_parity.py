@@ -346,3 +346,36 @@ def test_checkpoint_resume_is_bit_identical(built, prec, tmp_path):
     import json
     meta = json.load(open(prefix + ".json"))
     assert meta["shape"] == [W, 8, c.P] and len(meta["trace"]) == W and meta["windows"][0]["iterations"] == 12
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+@pytest.mark.parametrize("shape", [(58368, 40), (1048576, 128)])
+def test_full_size_additivity_over_row_blocks(built, prec, shape):
+    """Size-independent property at the full BASELINE sizes, where the CPU oracle would take minutes:
+    the likelihood part of log p and of the gradient is a sum over rows, so evaluating two row blocks
+    separately and adding must give the evaluation of the whole window.  A row's contribution does not
+    depend on the partition in either precision, so the tolerance is FP32 summation error."""
+    m, _ = built
+    rows, Hw = shape
+    Pw = 22 * Hw + 2 * Hw + 1
+    x, y, _ = m.synth_window(17, 3, rows, H=Hw)
+    w = _w(4, 0.1, Pw)
+    cfg = m.baseline_config(H=Hw, precision=prec)
+
+    def ev(xb, yb):
+        ctx = m.Context(cfg, n_windows=1, rows=xb.shape[0])
+        ctx.set_window_data(0, xb, yb)
+        out = ctx.potential_and_grad(0, w)
+        ctx.close()
+        return out
+
+    cut = rows // 2 + 77  # not a multiple of the tile size
+    full, a, b = ev(x, y), ev(x[:cut], y[:cut]), ev(x[cut:], y[cut:])
+    # the prior (gradient -w / s^2, s = 1 in this preset) is in every evaluation once
+    prior_grad = -w
+    lik_full = full["grad"] - prior_grad
+    lik_sum = (a["grad"] - prior_grad) + (b["grad"] - prior_grad)
+    scale = np.abs(lik_full).max()
+    assert np.abs(lik_full - lik_sum).max() <= 2e-5 * scale
+    assert abs(full["loglik"] - (a["loglik"] + b["loglik"])) <= 1e-6 * abs(full["loglik"])
+    assert full["logprior"] == a["logprior"] == b["logprior"]
