@@ -134,6 +134,9 @@ struct mcmc_b200_ctx {
   NcclComm comm = nullptr;
   int nranks = 1, rank = 0;
   long long launches = 0;
+  // all L leapfrog steps of an iteration in one cooperative launch (one window, TF32, H = 40)
+  bool multistep = false;
+  unsigned int* grid_bar = nullptr;
   float* dbg = nullptr;
   float* stage = nullptr;  // upload staging for one window: [rows][D] then [rows]
   std::vector<void*> allocs;
@@ -320,6 +323,15 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   // every CTA of the next launch summing all of them in its prologue
   c->use_red = c->slices > 4;
   c->use_red_x = c->slices_x > 4;
+  {
+    // one window on the whole GPU: run the L steps of an iteration as ONE cooperative launch (the CTAs
+    // meet at a grid barrier after every step).  Needs every CTA resident, the sums in `red` (use_red) and
+    // the free partition (a fixed `slices` asks for placement-independent bits: keep one launch per step).
+    const char* off = getenv("MCMC_B200_NO_MULTISTEP");
+    c->multistep = tf32 && n_windows == 1 && cfg->slices == 0 && c->use_red && cfg->leapfrog_steps >= 2 &&
+                   !(off && off[0] == '1') && c->tab_ctas > 0 && c->tab_ctas <= tf32_multistep_max_ctas(cfg->H) &&
+                   (c->P + c->tab_ctas - 1) / c->tab_ctas <= 8;
+  }
   const size_t W = n_windows, Pp = c->Pp, P = c->P;
   DA(c->xaug, W * c->rows_pad * KP * sizeof(float));
   for (int i = 0; i < 2; ++i) {
@@ -344,6 +356,7 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   DA(c->n_accept, W * 4);
   DA(c->gwin, W * 8);
   DA(c->status, 4);
+  DA(c->grid_bar, 4);
   DA(c->xg, Pp * 4);
   DA(c->g_out, Pp * 4);
   DA(c->row_loss, (size_t)c->rows_pad * 4);
@@ -605,11 +618,44 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   return MCMC_B200_OK;
 }
 
+// All L gradient evaluations of one iteration in one cooperative launch (chain_grad's L launches folded
+// into one; same buffers, same rotation).
+static int chain_grad_multistep(mcmc_b200_ctx* c, cudaStream_t st) {
+  GradParams g = base_grad_params(c);
+  g.slices_in = g.slices_out = c->slices;
+  g.nslot_in = c->tab_nslot;
+  g.seg_ptr = c->tab_seg_ptr;
+  g.segs = c->tab_segs;
+  g.g_carried = c->g_cur;
+  g.eps = c->eps;
+  g.n_steps = c->cfg.leapfrog_steps;
+  g.n_slots = c->slices;    // one window: the CTAs that own tiles of it, one partial vector each
+  for (int i = 0; i < 2; ++i) {
+    g.w_buf[i] = c->wbuf[i];
+    g.m_buf[i] = c->mbuf[i];
+    g.partial_buf[i] = c->partial[i];
+    g.ll_buf[i] = c->llp[i];
+  }
+  g.red = c->red;
+  g.grid_bar = c->grid_bar;
+  CK(cudaMemsetAsync(c->grid_bar, 0, 4, st));
+  cudaError_t e = launch_grad_tf32_multistep(c->cfg.H, &c->tmap_mn, g, c->tab_ctas, st);
+  c->launches++;
+  if (e != cudaSuccess)
+    return fail(MCMC_B200_ERR_CUDA, std::string("multi-step gradient kernel launch: ") + cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
 static int queue_iteration(mcmc_b200_ctx* c, cudaStream_t st) {
   const int L = c->cfg.leapfrog_steps;
-  for (int s = 0; s < L; ++s) {
-    int r = chain_grad(c, s == 0 ? MODE_FIRST : MODE_NEXT, s, st);
+  if (c->multistep) {
+    int r = chain_grad_multistep(c, st);
     if (r) return r;
+  } else {
+    for (int s = 0; s < L; ++s) {
+      int r = chain_grad(c, s == 0 ? MODE_FIRST : MODE_NEXT, s, st);
+      if (r) return r;
+    }
   }
   AcceptParams a = base_accept_params(c);
   fill_chain_accept(c, a, ACC_ITERATE, L);
@@ -679,7 +725,8 @@ API int mcmc_b200_run_chain_async(mcmc_b200_ctx* c, int n_iter) {
     cudaGetLastError();
     c->launches = launches_before;
   }
-  const long long per_iter = (long long)c->cfg.leapfrog_steps * ((c->comm || c->use_red) ? 2 : 1) + 1;
+  const long long per_iter =
+      c->multistep ? 2 : (long long)c->cfg.leapfrog_steps * ((c->comm || c->use_red) ? 2 : 1) + 1;
   for (int i = 0; i < n_iter; ++i) {
     if (c->graph_exec) {
       CK(cudaGraphLaunch(c->graph_exec, c->stream));
@@ -1083,6 +1130,7 @@ API int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* c, const unsigned char id[1
   }
   c->rank = rank;
   c->nranks = nranks;
+  c->multistep = false;  // every step's sums cross GPUs: one launch + one all-reduce per step
   return MCMC_B200_OK;
 }
 

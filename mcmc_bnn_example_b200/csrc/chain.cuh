@@ -74,6 +74,9 @@ int fp32_tile_rows(int H);
 cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
                              cudaStream_t st);
 int tf32_supported(int H);
+int tf32_multistep_max_ctas(int H);
+cudaError_t launch_grad_tf32_multistep(int H, const void* tmap_mn, const GradParams& g, int ctas,
+                                       cudaStream_t st);
 cudaError_t launch_grad_tf32_wide(const void* tmap_mn, const GradParams& g, int ctas, cudaStream_t st);
 constexpr int TF32_TILE = 128;
 

@@ -72,6 +72,17 @@ struct GradParams {
   PriorParams prior;
   int* status;              // device error word (bounded waits that ran out)
   int ablate;               // experiments only: bit mask of pipeline parts to skip (0 in production)
+  // several leapfrog steps in one cooperative launch (one window; grad_tf32.cu).  Step s reads
+  // w_buf/m_buf[s & 1], writes [(s + 1) & 1] and partial_buf/ll_buf[s & 1]; `red` receives the summed
+  // gradient after every step; grid_bar is a zeroed arrival counter
+  int n_steps;
+  int n_slots;              // CTAs that own tiles = partial vectors to sum
+  float* w_buf[2];
+  float* m_buf[2];
+  float* partial_buf[2];
+  double* ll_buf[2];
+  double* red;
+  unsigned int* grid_bar;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -113,18 +124,37 @@ __device__ __forceinline__ void lik_terms(const LikParams& lk, float y, float pr
 // (apply_leapfrog_step, mcmc_step_ffma.h:106-120; load_weights_bias :122-152):
 // every CTA of the window recomputes the same value from the same inputs in
 // the same order, slice 0 stores it.
-__device__ __forceinline__ float leapfrog_param(const GradParams& g, int win, int p, bool store) {
+// The state vectors and sums are read with ld.global.cg: inside a multi-step launch they were written by
+// other CTAs of the same kernel, and L1 is not coherent.
+struct StepIo {            // what changes from one leapfrog step to the next
+  const float* w_in;
+  const float* m_in;
+  float* w_out;
+  float* m_out;
+  const double* red_in;
+  int mode;
+};
+__device__ __forceinline__ StepIo step_io(const GradParams& g) {
+  return StepIo{g.w_in, g.m_in, g.w_out, g.m_out, g.red_in, g.mode};
+}
+// step s of a multi-step launch (chain_grad's buffer rotation)
+__device__ __forceinline__ StepIo step_io(const GradParams& g, int s) {
+  return StepIo{g.w_buf[s & 1], g.m_buf[s & 1], g.w_buf[(s + 1) & 1], g.m_buf[(s + 1) & 1],
+                s == 0 ? nullptr : g.red, s == 0 ? MODE_FIRST : MODE_NEXT};
+}
+__device__ __forceinline__ float leapfrog_param(const GradParams& g, const StepIo& io, int win, int p,
+                                                bool store) {
   const size_t o = (size_t)win * g.Pp + p;
-  float w = g.w_in[o];
-  if (g.mode == MODE_EVAL) return w;
+  float w = __ldcg(io.w_in + o);
+  if (io.mode == MODE_EVAL) return w;
   float grad;
   float kick;
-  if (g.mode == MODE_FIRST) {
+  if (io.mode == MODE_FIRST) {
     grad = g.g_carried[o];
     kick = 0.5f;
   } else {
-    if (g.red_in) {
-      grad = (float)g.red_in[(size_t)win * (g.Pp + 4) + p];
+    if (io.red_in) {
+      grad = (float)__ldcg(io.red_in + (size_t)win * (g.Pp + 4) + p);
     } else {
       const float* pi = g.partial_in + (size_t)win * g.slices_in * g.Pp + p;
       const int ns = g.nslot_in ? g.nslot_in[win] : g.slices_in;
@@ -135,14 +165,17 @@ __device__ __forceinline__ float leapfrog_param(const GradParams& g, int win, in
     kick = 1.f;
   }
   const float eps = g.eps ? g.eps[win] : g.eps_scalar;
-  float m = g.m_in[o];
+  float m = __ldcg(io.m_in + o);
   m = fmaf(eps * kick, grad, m);
   w = fmaf(eps, m, w);
   if (store) {
-    g.w_out[o] = w;
-    g.m_out[o] = m;
+    io.w_out[o] = w;
+    io.m_out[o] = m;
   }
   return w;
+}
+__device__ __forceinline__ float leapfrog_param(const GradParams& g, int win, int p, bool store) {
+  return leapfrog_param(g, step_io(g), win, p, store);
 }
 
 // ---- mbarrier / bulk-copy wrappers --------------------------------------
@@ -238,6 +271,37 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
   uint64_t d;
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
+}
+
+// ---- grid-wide barrier of a cooperative launch --------------------------------
+// Every CTA of the grid is resident (the launch is cooperative), so the wait always ends; it is bounded
+// all the same: after about 0.2 s the leader records `code`, and every later barrier of this CTA returns at
+// once so that the kernel runs to its end (with results that the status word marks as invalid).
+// `target` = arrivals expected in total at this barrier = (barriers passed so far + 1) * gridDim.x.
+__device__ __forceinline__ bool grid_barrier(unsigned int* cnt, unsigned int target, bool leader, bool& alive,
+                                             int* status, int code) {
+  __shared__ int s_alive;
+  __syncthreads();
+  if (leader) {
+    bool ok = alive;
+    if (ok) {
+      __threadfence();
+      atomicAdd(cnt, 1u);
+      unsigned int seen = 0;
+      for (int it = 0; it < (1 << 21); ++it) {
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
+        if (seen >= target) break;
+        __nanosleep(64);
+      }
+      ok = seen >= target;
+      if (!ok && status) atomicExch(status, code);
+      __threadfence();
+    }
+    s_alive = ok ? 1 : 0;
+  }
+  __syncthreads();
+  alive = s_alive != 0;
+  return alive;
 }
 
 // ---- programmatic dependent launch -----------------------------------------

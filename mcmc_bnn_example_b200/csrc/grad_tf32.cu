@@ -114,7 +114,43 @@ struct Tf32Geom {
 #define PROF_FLUSH
 #endif
 
-template <int H>
+// One CTA's share of the cross-CTA sum inside a multi-step launch: parameters
+// [blockIdx.x * per_cta, ...) summed over the n_slots partial vectors in a fixed order (48 slot lanes per
+// parameter, then the lanes in order).  Called by the 384 compute threads.
+__device__ __forceinline__ void sum_partials_slice(const GradParams& g, const float* partial_out,
+                                                const double* ll_out, float* sc /* [8][48] */, int tid) {
+  constexpr int LANES = 48, NCOMPUTE = TF32_NWG * 128;
+  const int nb = (int)gridDim.x;
+  const int per_cta = (g.P + nb - 1) / nb;  // <= 8 for 961 parameters on >= 121 CTAs
+  const int q = tid / LANES, sl = tid % LANES;
+  const int p = (int)blockIdx.x * per_cta + q;
+  float acc = 0.f;
+  if (q < per_cta && p < g.P) {
+    const float* src = partial_out + p;
+    for (int sidx = sl; sidx < g.n_slots; sidx += LANES) acc += __ldcg(src + (size_t)sidx * g.Pp);
+  }
+  sc[q * LANES + sl] = acc;
+  named_sync(1, NCOMPUTE);  // the compute warpgroups only
+  if (sl == 0 && q < per_cta && p < g.P) {
+    float t = 0.f;
+#pragma unroll 8
+    for (int k = 0; k < LANES; ++k) t += sc[q * LANES + k];
+    g.red[p] = (double)t;
+  }
+  if (blockIdx.x == (unsigned)(nb - 1) && tid == NCOMPUTE - 1) {  // log-likelihood, and the padding of the sums
+    double l = 0.0;
+    for (int sidx = 0; sidx < g.n_slots; ++sidx) l += __ldcg(ll_out + sidx);
+    g.red[g.Pp] = l;
+    for (int k = g.P; k < g.Pp; ++k) g.red[k] = 0.0;
+  }
+}
+
+// MULTI = several leapfrog steps of ONE window in one cooperative launch (GradParams::n_steps): after
+// every step the CTAs meet at a grid-wide barrier, each CTA sums a few parameters' partials over all
+// CTAs into GradParams::red, they meet again, and the next step's prologue reads the sums.  This is
+// the reference's persistent-kernel structure (mcmc_step_kernel + sync_and_swap,
+// mcmc_step_tc.h:597-677) with a bounded barrier and a fixed-order sum instead of atomics.
+template <int H, bool MULTI>
 __global__ void __launch_bounds__(TF32_THREADS, 1)
 grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g, float* dbg) {
   using G = Tf32Geom<H>;
@@ -137,6 +173,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   __shared__ float red_w1[NWG][H];
   __shared__ float red_db1[NWG * 4];
   __shared__ double red_ll[NWG * 4];
+  __shared__ float red_sc[MULTI ? 8 : 1][48];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -172,6 +209,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   const uint32_t w0s_addr = smem_u32(w0s);
   const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];  // host-written table
   bool ok = true;
+  const int n_steps = MULTI ? g.n_steps : 1;
   // everything above is private set-up; from here on the kernel reads what its predecessor wrote
   pdl_trigger();
   pdl_wait();
@@ -182,6 +220,8 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     // =====================  control warpgroup (warps 12..15; warp 15 only keeps the barriers) ==========
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TF32_CTRL_REGS));
     uint32_t c_issued = 0;  // tiles of this warpgroup whose MMAs have been issued (mbarrier phases follow it)
+    bool alive = true;
+    for (int step = 0; step < n_steps; ++step) {
     for (int sg = seg0; sg < seg1; ++sg) {
       const int4 seg = g.segs[sg];
       const int win = seg.x, t0 = seg.y, nt = seg.z - seg.y;
@@ -245,6 +285,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       __syncthreads();  // S2
       __syncthreads();  // S3
     }
+    if (MULTI) {  // the two grid-wide barriers of a step: this role only keeps the CTA barriers inside them
+      grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
+      if (step + 1 < n_steps) grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
+    }
+    }
   } else {
     // =====================  compute warpgroups: one row per thread  =====================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TF32_COMPUTE_REGS));
@@ -262,7 +307,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     // rows r and r+4 of a staged tile keep their 32-byte chunks in the same banks: the upper four of
     // every eight rows read the two halves of a chunk in the opposite order
     const bool swap_halves = (wtid & 4) != 0;
+    bool alive = true;
 
+    for (int step = 0; step < n_steps; ++step) {
     for (int sg = seg0; sg < seg1; ++sg) {
       const int4 seg = g.segs[sg];
       const int win = seg.x, t0 = seg.y, t1 = seg.z, slot = seg.w;
@@ -280,8 +327,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         }
       }
       // element (n = hidden unit, k) of the K-major B operand at n*128 + ((k/4) ^ (n%8))*16 + (k%4)*4
+      const StepIo io = MULTI ? step_io(g, step) : step_io(g);
       for (int p = tid; p < G::P; p += NCOMPUTE) {
-        const float w = leapfrog_param(g, win, p, slot == 0);
+        const float w = leapfrog_param(g, io, win, p, slot == 0);
         if (p < D * H + H) {
           const int k = p / H, n = p - k * H;
           *reinterpret_cast<float*>(w0s + n * 128 + (((k >> 2) ^ (n & 7)) << 4) + ((k & 3) << 2)) = w;
@@ -453,7 +501,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       __syncthreads();  // S2
 
       // ---- segment read-out: one partial gradient vector for (window, slot) ----
-      float* po = g.partial_out + ((size_t)win * g.slices_out + slot) * g.Pp;
+      float* po = (MULTI ? g.partial_buf[step & 1] : g.partial_out) + ((size_t)win * g.slices_out + slot) * g.Pp;
       if (warp < 4) {
         tc_fence_after();
         float gacc[NB];
@@ -498,10 +546,18 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           double l = 0.0;
           for (int w = 0; w < NWG * 4; ++w) { s += red_db1[w]; l += red_ll[w]; }
           po[D * H + 2 * H] = s;
-          g.ll_out[(size_t)win * g.slices_out + slot] = l;
+          (MULTI ? g.ll_buf[step & 1] : g.ll_out)[(size_t)win * g.slices_out + slot] = l;
         }
       }
       __syncthreads();  // S3: read-out done before the next segment restages W0a / reuses the scratch
+    }
+    if (MULTI) {
+      // ---- all partial vectors of this step are written: sum them, a few parameters per CTA ----
+      const unsigned int nb = gridDim.x;
+      grid_barrier(g.grid_bar, (2u * step + 1u) * nb, tid == 0, alive, g.status, 401);
+      sum_partials_slice(g, g.partial_buf[step & 1], g.ll_buf[step & 1], &red_sc[0][0], tid);
+      if (step + 1 < n_steps) grid_barrier(g.grid_bar, (2u * step + 2u) * nb, tid == 0, alive, g.status, 402);
+    }
     }
   }
 
@@ -525,13 +581,51 @@ static cudaError_t launch_tf32_t(const void* tmap_mn, const GradParams& g, int c
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !attr_done[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(grad_tf32_kernel<H>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)G::SMEM);
+    cudaError_t e = cudaFuncSetAttribute(grad_tf32_kernel<H, false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G::SMEM);
     if (e != cudaSuccess) return e;
     attr_done[dev] = true;
   }
-  return launch_chain_kernel(grad_tf32_kernel<H>, dim3(ctas), dim3(TF32_THREADS), G::SMEM, st,
+  return launch_chain_kernel(grad_tf32_kernel<H, false>, dim3(ctas), dim3(TF32_THREADS), G::SMEM, st,
                              *reinterpret_cast<const CUtensorMap*>(tmap_mn), g, dbg);
+}
+
+// Several leapfrog steps of one window in one COOPERATIVE launch (every CTA resident: the grid barrier
+// inside relies on it).  Returns cudaErrorCooperativeLaunchTooLarge-like errors to the caller, which then
+// falls back to one launch per step.
+int tf32_multistep_max_ctas(int H) {
+  if (H != 40) return 0;
+  using G = Tf32Geom<40>;
+  int dev = 0, coop = 0, sms = 0, per_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (!coop) return 0;
+  if (cudaFuncSetAttribute(grad_tf32_kernel<40, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (int)G::SMEM) != cudaSuccess)
+    return 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, grad_tf32_kernel<40, true>, TF32_THREADS,
+                                                    G::SMEM) != cudaSuccess)
+    return 0;
+  return per_sm * sms;
+}
+
+cudaError_t launch_grad_tf32_multistep(int H, const void* tmap_mn, const GradParams& g, int ctas,
+                                       cudaStream_t st) {
+  if (H != 40) return cudaErrorInvalidValue;
+  using G = Tf32Geom<40>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctas);
+  cfg.blockDim = dim3(TF32_THREADS);
+  cfg.dynamicSmemBytes = G::SMEM;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, grad_tf32_kernel<40, true>, *reinterpret_cast<const CUtensorMap*>(tmap_mn), g,
+                            (float*)nullptr);
 }
 
 cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
