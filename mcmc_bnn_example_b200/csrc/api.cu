@@ -25,6 +25,9 @@ using namespace mcmc_b200;
 #define API extern "C" __attribute__((visibility("default")))
 
 static thread_local std::string g_last_error;
+// the one-launch-per-iteration path for single-window contexts: opt-in (MCMC_B200_MULTISTEP=1) while
+// false, opt-out (MCMC_B200_NO_MULTISTEP=1) while true
+static constexpr bool MULTISTEP_DEFAULT = false;
 
 static int fail(int code, const std::string& msg) {
   g_last_error = msg;
@@ -328,8 +331,10 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
     // meet at a grid barrier after every step).  Needs every CTA resident, the sums in `red` (use_red) and
     // the free partition (a fixed `slices` asks for placement-independent bits: keep one launch per step).
     const char* off = getenv("MCMC_B200_NO_MULTISTEP");
+    const char* on = getenv("MCMC_B200_MULTISTEP");
+    const bool want = MULTISTEP_DEFAULT ? !(off && off[0] == '1') : (on && on[0] == '1');
     c->multistep = tf32 && n_windows == 1 && cfg->slices == 0 && c->use_red && cfg->leapfrog_steps >= 2 &&
-                   !(off && off[0] == '1') && c->tab_ctas > 0 && c->tab_ctas <= tf32_multistep_max_ctas(cfg->H) &&
+                   want && c->tab_ctas > 0 && c->tab_ctas <= tf32_multistep_max_ctas(cfg->H) &&
                    (c->P + c->tab_ctas - 1) / c->tab_ctas <= 8;
   }
   const size_t W = n_windows, Pp = c->Pp, P = c->P;

@@ -379,3 +379,42 @@ def test_full_size_additivity_over_row_blocks(built, prec, shape):
     assert np.abs(lik_full - lik_sum).max() <= 2e-5 * scale
     assert abs(full["loglik"] - (a["loglik"] + b["loglik"])) <= 1e-6 * abs(full["loglik"])
     assert full["logprior"] == a["logprior"] == b["logprior"]
+
+
+def test_multistep_launch_matches_per_step_launches(built, monkeypatch):
+    """One window in TF32 mode runs the L leapfrog steps of an iteration as ONE cooperative launch (grid
+    barrier + cross-CTA sum inside the kernel).  The same chain with one launch per step must agree: same
+    accept decisions, states equal up to the order of the cross-CTA sums."""
+    m, O = built
+    rows, n_iter = 58368, 12
+    x, y, _ = m.synth_window(41, 0, rows)
+    x = x * np.float32(0.05)
+
+    def run():
+        cfg = m.reference_config(precision=m.PREC_TF32, leapfrog_steps=10, burn_in=0, adapt_steps=8,
+                                 sample_capacity=n_iter, trace_iters=n_iter, seed=7, eps0=0.02)
+        ctx = m.Context(cfg, n_windows=1, rows=rows)
+        ctx.set_window_data(0, x, y)
+        n0 = ctx.launch_count(reset=True)
+        ctx.run_chain(n_iter)
+        out = (ctx.get_samples(0), ctx.get_trace(0), ctx.chain_info(0), ctx.launch_count())
+        ctx.close()
+        return out
+
+    monkeypatch.setenv("MCMC_B200_MULTISTEP", "1")
+    monkeypatch.delenv("MCMC_B200_NO_MULTISTEP", raising=False)
+    s_multi, t_multi, i_multi, l_multi = run()
+    monkeypatch.delenv("MCMC_B200_MULTISTEP")
+    monkeypatch.setenv("MCMC_B200_NO_MULTISTEP", "1")
+    s_step, t_step, i_step, l_step = run()
+    assert l_multi < l_step  # 2 launches per iteration instead of 21
+    assert i_multi == i_step
+    assert np.array_equal(t_multi["accepted"], t_step["accepted"])
+    assert 0 < t_multi["accepted"].sum()
+    assert np.allclose(t_multi["log_acpt"], t_step["log_acpt"], rtol=1e-3, atol=1e-3)
+    assert np.abs(s_multi - s_step).max() <= 1e-4 * np.abs(s_step).max()
+    # and against the oracle with the device's draws
+    ref = O.hmc_chain(O.reference_model(tf32=True), O.Sampler(10, 8, 0.02, 0.2, 0.1, 0.01), x, y,
+                      t_multi["momenta"], t_multi["log_u"])
+    clear = np.abs(ref["log_acpt"] - t_multi["log_u"]) > 0.05
+    assert np.array_equal(ref["accepted"][clear], t_multi["accepted"][clear])
