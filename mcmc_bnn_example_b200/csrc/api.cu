@@ -335,7 +335,7 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
     const bool want = MULTISTEP_DEFAULT ? !(off && off[0] == '1') : (on && on[0] == '1');
     c->multistep = tf32 && n_windows == 1 && cfg->slices == 0 && c->use_red && cfg->leapfrog_steps >= 2 &&
                    want && c->tab_ctas > 0 && c->tab_ctas <= tf32_multistep_max_ctas(cfg->H) &&
-                   (c->P + c->tab_ctas - 1) / c->tab_ctas <= 8;
+                   (c->P + c->tab_ctas - 1) / c->tab_ctas <= 12;
   }
   const size_t W = n_windows, Pp = c->Pp, P = c->P;
   DA(c->xaug, W * c->rows_pad * KP * sizeof(float));

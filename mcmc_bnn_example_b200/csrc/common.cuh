@@ -139,7 +139,10 @@ __device__ __forceinline__ StepIo step_io(const GradParams& g) {
 }
 // step s of a multi-step launch (chain_grad's buffer rotation)
 __device__ __forceinline__ StepIo step_io(const GradParams& g, int s) {
-  return StepIo{g.w_buf[s & 1], g.m_buf[s & 1], g.w_buf[(s + 1) & 1], g.m_buf[(s + 1) & 1],
+  // (constant indices under a select: a dynamic index would move the parameter arrays to local memory)
+  const bool odd = (s & 1) != 0;
+  return StepIo{odd ? g.w_buf[1] : g.w_buf[0], odd ? g.m_buf[1] : g.m_buf[0],
+                odd ? g.w_buf[0] : g.w_buf[1], odd ? g.m_buf[0] : g.m_buf[1],
                 s == 0 ? nullptr : g.red, s == 0 ? MODE_FIRST : MODE_NEXT};
 }
 __device__ __forceinline__ float leapfrog_param(const GradParams& g, const StepIo& io, int win, int p,
@@ -275,7 +278,7 @@ __device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
 
 // ---- grid-wide barrier of a cooperative launch --------------------------------
 // Every CTA of the grid is resident (the launch is cooperative), so the wait always ends; it is bounded
-// all the same: after about 0.2 s the leader records `code`, and every later barrier of this CTA returns at
+// all the same: after about 0.3 s the leader records `code`, and every later barrier of this CTA returns at
 // once so that the kernel runs to its end (with results that the status word marks as invalid).
 // `target` = arrivals expected in total at this barrier = (barriers passed so far + 1) * gridDim.x.
 __device__ __forceinline__ bool grid_barrier(unsigned int* cnt, unsigned int target, bool leader, bool& alive,
@@ -288,10 +291,9 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* cnt, unsigned int tar
       __threadfence();
       atomicAdd(cnt, 1u);
       unsigned int seen = 0;
-      for (int it = 0; it < (1 << 21); ++it) {
+      for (int it = 0; it < (1 << 19); ++it) {  // one L2 round trip per poll: about 0.3 s in all
         asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(cnt) : "memory");
         if (seen >= target) break;
-        __nanosleep(64);
       }
       ok = seen >= target;
       if (!ok && status) atomicExch(status, code);

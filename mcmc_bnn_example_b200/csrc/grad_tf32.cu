@@ -115,33 +115,32 @@ struct Tf32Geom {
 #endif
 
 // One CTA's share of the cross-CTA sum inside a multi-step launch: parameters
-// [blockIdx.x * per_cta, ...) summed over the n_slots partial vectors in a fixed order (48 slot lanes per
-// parameter, then the lanes in order).  Called by the 384 compute threads.
+// [blockIdx.x * per_cta, ...) summed over the n_slots partial vectors in a fixed order (one warp per
+// parameter: lane l adds slots l, l+32, ..., then a shuffle tree).  Called by the 12 compute warps.
 __device__ __forceinline__ void sum_partials_slice(const GradParams& g, const float* partial_out,
-                                                const double* ll_out, float* sc /* [8][48] */, int tid) {
-  constexpr int LANES = 48, NCOMPUTE = TF32_NWG * 128;
+                                                   const double* ll_out, int tid) {
   const int nb = (int)gridDim.x;
-  const int per_cta = (g.P + nb - 1) / nb;  // <= 8 for 961 parameters on >= 121 CTAs
-  const int q = tid / LANES, sl = tid % LANES;
+  const int per_cta = (g.P + nb - 1) / nb;  // <= 12 (one per compute warp)
+  const int q = tid >> 5, lane = tid & 31;
   const int p = (int)blockIdx.x * per_cta + q;
-  float acc = 0.f;
   if (q < per_cta && p < g.P) {
     const float* src = partial_out + p;
-    for (int sidx = sl; sidx < g.n_slots; sidx += LANES) acc += __ldcg(src + (size_t)sidx * g.Pp);
+    float acc = 0.f;
+#pragma unroll 5
+    for (int sidx = lane; sidx < g.n_slots; sidx += 32) acc += __ldcg(src + (size_t)sidx * g.Pp);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) g.red[p] = (double)acc;
   }
-  sc[q * LANES + sl] = acc;
-  named_sync(1, NCOMPUTE);  // the compute warpgroups only
-  if (sl == 0 && q < per_cta && p < g.P) {
-    float t = 0.f;
-#pragma unroll 8
-    for (int k = 0; k < LANES; ++k) t += sc[q * LANES + k];
-    g.red[p] = (double)t;
-  }
-  if (blockIdx.x == (unsigned)(nb - 1) && tid == NCOMPUTE - 1) {  // log-likelihood, and the padding of the sums
+  if (blockIdx.x == (unsigned)(nb - 1) && q == 11) {  // log-likelihood, and the padding of the sum vector
     double l = 0.0;
-    for (int sidx = 0; sidx < g.n_slots; ++sidx) l += __ldcg(ll_out + sidx);
-    g.red[g.Pp] = l;
-    for (int k = g.P; k < g.Pp; ++k) g.red[k] = 0.0;
+    for (int sidx = lane; sidx < g.n_slots; sidx += 32) l += __ldcg(ll_out + sidx);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) {
+      g.red[g.Pp] = l;
+      for (int k = g.P; k < g.Pp; ++k) g.red[k] = 0.0;
+    }
   }
 }
 
@@ -173,7 +172,6 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   __shared__ float red_w1[NWG][H];
   __shared__ float red_db1[NWG * 4];
   __shared__ double red_ll[NWG * 4];
-  __shared__ float red_sc[MULTI ? 8 : 1][48];
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -209,7 +207,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   const uint32_t w0s_addr = smem_u32(w0s);
   const int seg0 = g.seg_ptr[blockIdx.x], seg1 = g.seg_ptr[blockIdx.x + 1];  // host-written table
   bool ok = true;
-  const int n_steps = MULTI ? g.n_steps : 1;
+  // (every CTA of a multi-step launch owns at least one segment: the host only uses it when all CTAs have tiles)
+  const int nseg = seg1 - seg0;
+  const int n_iters = MULTI ? g.n_steps * nseg : nseg;
   // everything above is private set-up; from here on the kernel reads what its predecessor wrote
   pdl_trigger();
   pdl_wait();
@@ -221,8 +221,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TF32_CTRL_REGS));
     uint32_t c_issued = 0;  // tiles of this warpgroup whose MMAs have been issued (mbarrier phases follow it)
     bool alive = true;
-    for (int step = 0; step < n_steps; ++step) {
-    for (int sg = seg0; sg < seg1; ++sg) {
+    // a multi-step launch walks its segments once per step: ONE loop over (step, segment) pairs
+    for (int it = 0; it < n_iters; ++it) {
+      const int sg = MULTI ? seg0 + it % nseg : seg0 + it;
       const int4 seg = g.segs[sg];
       const int win = seg.x, t0 = seg.y, nt = seg.z - seg.y;
       const int grow0 = (g.data_window0 + win) * rows_pad;
@@ -284,11 +285,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       }
       __syncthreads();  // S2
       __syncthreads();  // S3
-    }
-    if (MULTI) {  // the two grid-wide barriers of a step: this role only keeps the CTA barriers inside them
-      grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
-      if (step + 1 < n_steps) grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
-    }
+      if (MULTI && (it + 1) % nseg == 0) {
+        // the two grid-wide barriers of a step: this role only keeps the CTA barriers inside them
+        grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
+        if (it + 1 < n_iters) grid_barrier(g.grid_bar, 0u, false, alive, g.status, 0);
+      }
     }
   } else {
     // =====================  compute warpgroups: one row per thread  =====================================
@@ -309,8 +310,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     const bool swap_halves = (wtid & 4) != 0;
     bool alive = true;
 
-    for (int step = 0; step < n_steps; ++step) {
-    for (int sg = seg0; sg < seg1; ++sg) {
+    for (int it = 0; it < n_iters; ++it) {
+      const int sg = MULTI ? seg0 + it % nseg : seg0 + it;
+      const int step = MULTI ? it / nseg : 0;
       const int4 seg = g.segs[sg];
       const int win = seg.x, t0 = seg.y, t1 = seg.z, slot = seg.w;
       const int nt = t1 - t0;
@@ -501,7 +503,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       __syncthreads();  // S2
 
       // ---- segment read-out: one partial gradient vector for (window, slot) ----
-      float* po = (MULTI ? g.partial_buf[step & 1] : g.partial_out) + ((size_t)win * g.slices_out + slot) * g.Pp;
+      float* po = (MULTI ? ((step & 1) ? g.partial_buf[1] : g.partial_buf[0]) : g.partial_out) + ((size_t)win * g.slices_out + slot) * g.Pp;
       if (warp < 4) {
         tc_fence_after();
         float gacc[NB];
@@ -546,18 +548,18 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           double l = 0.0;
           for (int w = 0; w < NWG * 4; ++w) { s += red_db1[w]; l += red_ll[w]; }
           po[D * H + 2 * H] = s;
-          (MULTI ? g.ll_buf[step & 1] : g.ll_out)[(size_t)win * g.slices_out + slot] = l;
+          (MULTI ? ((step & 1) ? g.ll_buf[1] : g.ll_buf[0]) : g.ll_out)[(size_t)win * g.slices_out + slot] = l;
         }
       }
       __syncthreads();  // S3: read-out done before the next segment restages W0a / reuses the scratch
-    }
-    if (MULTI) {
-      // ---- all partial vectors of this step are written: sum them, a few parameters per CTA ----
-      const unsigned int nb = gridDim.x;
-      grid_barrier(g.grid_bar, (2u * step + 1u) * nb, tid == 0, alive, g.status, 401);
-      sum_partials_slice(g, g.partial_buf[step & 1], g.ll_buf[step & 1], &red_sc[0][0], tid);
-      if (step + 1 < n_steps) grid_barrier(g.grid_bar, (2u * step + 2u) * nb, tid == 0, alive, g.status, 402);
-    }
+      if (MULTI && (it + 1) % nseg == 0) {
+        // ---- all partial vectors of this step are written: sum them, a few parameters per CTA ----
+        const unsigned int nb = gridDim.x;
+        grid_barrier(g.grid_bar, (2u * step + 1u) * nb, tid == 0, alive, g.status, 401);
+        sum_partials_slice(g, (step & 1) ? g.partial_buf[1] : g.partial_buf[0],
+                           (step & 1) ? g.ll_buf[1] : g.ll_buf[0], tid);
+        if (it + 1 < n_iters) grid_barrier(g.grid_bar, (2u * step + 2u) * nb, tid == 0, alive, g.status, 402);
+      }
     }
   }
 
