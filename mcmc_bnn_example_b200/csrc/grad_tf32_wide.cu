@@ -353,7 +353,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
           float v[CH];
           tc_ld32(z_t + c * CH, v);
           tc_wait_ld();
-          float p0 = 0.f, p1 = 0.f;
+          uint64_t pp0 = 0ull, pp1 = 0ull;  // packed f32x2 accumulators of the output layer
 #pragma unroll
           for (int j = 0; j < CH; j += 4) {
             const float4 w1v = *reinterpret_cast<const float4*>(w1s + c * CH + j);  // broadcast read
@@ -361,12 +361,13 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
             v[j + 1] = tanh_fast(v[j + 1]);
             v[j + 2] = tanh_fast(v[j + 2]);
             v[j + 3] = tanh_fast(v[j + 3]);
-            p0 = fmaf(w1v.x, v[j], p0);
-            p1 = fmaf(w1v.y, v[j + 1], p1);
-            p0 = fmaf(w1v.z, v[j + 2], p0);
-            p1 = fmaf(w1v.w, v[j + 3], p1);
+            pp0 = fma2(pack2(w1v.x, w1v.y), pack2(v[j], v[j + 1]), pp0);
+            pp1 = fma2(pack2(w1v.z, w1v.w), pack2(v[j + 2], v[j + 3]), pp1);
           }
-          pred += p0 + p1;
+          float q0, q1, q2, q3;
+          unpack2(pp0, q0, q1);
+          unpack2(pp1, q2, q3);
+          pred += (q0 + q1) + (q2 + q3);
           tc_st32(z_t + c * CH, v);
         }
         tc_wait_st();
@@ -396,11 +397,13 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
             publish_row();
           }
           float e[CH];
+          const uint64_t dy2 = pack2(dy, dy), ndy2 = pack2(ndy, ndy);
 #pragma unroll
-          for (int j = 0; j < CH; ++j) {
-            const float h = v[j];
-            e[j] = fmaf(h * h, ndy, dy);  // (1 - h^2) dy; the W1 factor is applied at read-out
-            v[j] = dy * h;
+          for (int j = 0; j < CH; j += 2) {
+            const uint64_t h2 = pack2(v[j], v[j + 1]);
+            // (1 - h^2) dy = dy - (h h) dy; the W1 factor is applied at read-out
+            unpack2(fma2(mul2(h2, h2), ndy2, dy2), e[j], e[j + 1]);
+            unpack2(mul2(dy2, h2), v[j], v[j + 1]);
           }
           if (c == 0) store_e_wide<0>(e_ptr, e, std::make_integer_sequence<int, CH>{});
           if (c == 1) store_e_wide<1>(e_ptr, e, std::make_integer_sequence<int, CH>{});

@@ -54,6 +54,30 @@ def test_gradient_matches_finite_differences(model):
     assert abs(O.logp_f64(model, x, y, w64) - (r["loglik"] + r["logprior"])) < 1e-6 * abs(r["loglik"])
 
 
+@pytest.mark.parametrize("tf32", [False, True])
+def test_wide_model_gradient_matches_finite_differences(tf32):
+    """22 -> 128 -> 1 (3073 parameters, the scaled stress configuration): the oracle's gradient against
+    central differences of its own double-precision log density; the TF32 mode within its tolerance."""
+    Hw = 128
+    Pw = O.num_params(D, Hw)
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((200, D)).astype(np.float32)
+    y = rng.standard_normal(200).astype(np.float32)
+    w = (0.1 * rng.standard_normal(Pw)).astype(np.float32)
+    exact = O.baseline_model(H=Hw)
+    r = O.logp_grad(O.baseline_model(tf32=tf32, H=Hw), x, y, w)
+    w64 = w.astype(np.float64)
+    scale = np.abs(r["grad"]).max()
+    tol = 2e-3 if tf32 else 2e-6
+    for p in rng.choice(Pw, 30, replace=False):
+        h = 1e-4
+        wp, wm = w64.copy(), w64.copy()
+        wp[p] += h
+        wm[p] -= h
+        fd = (O.logp_f64(exact, x, y, wp) - O.logp_f64(exact, x, y, wm)) / (2 * h)
+        assert abs(fd - r["grad"][p]) <= tol * scale + 1e-6 * abs(fd)
+
+
 def test_zero_weights_only_output_bias_gets_likelihood_gradient():
     # tanh(0) = 0 and W1 = 0: every likelihood gradient vanishes except db1 = sum dL/dpred
     x, y, _ = _data(64, 3)
