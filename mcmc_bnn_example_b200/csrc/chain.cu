@@ -23,7 +23,6 @@ constexpr int ACC_THREADS = 256;
 __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptParams a) {
   __shared__ double dsc[32];
   __shared__ int s_accept;
-  __shared__ float s_eps;
   const int win = blockIdx.x;
   const int tid = threadIdx.x;
   const size_t o = (size_t)win * a.Pp;
@@ -113,7 +112,7 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
       a.lp_cur[win] = lp_new;
     }
     s_accept = acc;
-    s_eps = eps_next;
+
   }
   __syncthreads();
   const int acc = s_accept;
