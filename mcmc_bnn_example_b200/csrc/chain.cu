@@ -112,7 +112,6 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
       a.lp_cur[win] = lp_new;
     }
     s_accept = acc;
-
   }
   __syncthreads();
   const int acc = s_accept;
