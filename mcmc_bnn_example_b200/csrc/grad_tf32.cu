@@ -83,7 +83,7 @@ struct Tf32Geom {
   static constexpr int TMEM_COLS = 512;
   static_assert(H % 8 == 0 && H <= 64, "hidden width must be a multiple of 8, at most 64");
   static_assert(G_COL0 + TF32_NWG * G_STRIDE <= TMEM_COLS, "tensor memory budget");
-  static_assert(128 * (H + 1) * 4 <= TF32_NST * TILE_BYTES, "dW1 reduction scratch aliases the row tiles");
+  static_assert(H > 32 && ((H - 32) & (H - 33)) == 0, "the dW1 butterfly handles 32 + a power of two units");
   static_assert(ES_ATOM_BYTES % 1024 == 0, "E atoms must keep the 1024-byte swizzle alignment");
 };
 
@@ -169,7 +169,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   __shared__ __align__(8) uint64_t bar_fwd[NWG], bar_bwd[NWG];
   __shared__ uint32_t tmem_slot;
   __shared__ float b1s;
-  __shared__ float red_w1[NWG][H];
+  __shared__ float red_w1[NWG * 4][H];
   __shared__ float red_db1[NWG * 4];
   __shared__ double red_ll[NWG * 4];
 
@@ -474,16 +474,33 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       PROF_FLUSH
       n_done += my_nt;
 
-      // ---- this warpgroup's share of dW1 / db1 / log-lik (its row-tile stages are free now: scratch) ----
+      // ---- this warp's share of dW1 / db1 / log-lik ----
       if (n_done > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n_done - 1) & 1, g.status, 204);
       tc_fence_after();
-      float* sc = reinterpret_cast<float*>(xb + wg * NST * G::TILE_BYTES);
+      {
+        // column sums over the warp's 32 rows: a halving butterfly leaves hidden unit `lane` in lane `lane`
+        // (units 0..31); the last H - 32 units take three halving steps and two plain ones
+        float v[H];
 #pragma unroll
-      for (int j = 0; j < H; j += 2) {
-        float a, b;
-        unpack2(dw1p[j >> 1], a, b);
-        sc[wtid * (H + 1) + j] = a;
-        sc[wtid * (H + 1) + j + 1] = b;
+        for (int j = 0; j < H; j += 2) unpack2(dw1p[j >> 1], v[j], v[j + 1]);
+        const float s_lo = warp_column_sums(v, lane);
+        constexpr int REST = H - 32;  // 8
+        float* u = v + 32;
+#pragma unroll
+        for (int off = REST / 2; off > 0; off >>= 1) {
+          const bool up = (lane & off) != 0;
+#pragma unroll
+          for (int i = 0; i < off; ++i) {
+            const float send = up ? u[i] : u[i + off];
+            const float keep = up ? u[i + off] : u[i];
+            u[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+          }
+        }
+        float s_hi = u[0];
+#pragma unroll
+        for (int off = REST; off < 32; off <<= 1) s_hi += __shfl_xor_sync(0xffffffffu, s_hi, off);
+        red_w1[warp][lane] = s_lo;
+        if (lane < REST) red_w1[warp][32 + lane] = s_hi;
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
@@ -493,12 +510,6 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       if (lane == 0) {
         red_db1[warp] = db1;
         red_ll[warp] = llacc;
-      }
-      named_sync(wg + 1, 128);  // this warpgroup only
-      if (wtid < H) {
-        float s = 0.f;
-        for (int r = 0; r < 128; ++r) s += sc[r * (H + 1) + wtid];
-        red_w1[wg][wtid] = s;
       }
       __syncthreads();  // S2
 
@@ -540,7 +551,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         for (int j = lane; j < H; j += 32) {
           float s = red_w1[0][j];
 #pragma unroll
-          for (int w = 1; w < NWG; ++w) s += red_w1[w][j];
+          for (int w = 1; w < NWG * 4; ++w) s += red_w1[w][j];
           po[D * H + H + j] = s;
         }
         if (lane == 0) {

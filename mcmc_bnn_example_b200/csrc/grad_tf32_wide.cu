@@ -103,23 +103,6 @@ __device__ __forceinline__ void store_e_wide(const uint32_t* e_ptr, const float*
   (store_e_wide_one<C, Js>(e_ptr, v), ...);
 }
 
-// Sum of v[j] over the 32 lanes of the warp, for every j = 0..31: lane l returns the sum for j = l.
-// Step `off` (16, 8, 4, 2, 1): a lane whose bit `off` is clear keeps the lower half of its remaining values
-// and sends the upper half to lane ^ off, which does the opposite.
-__device__ __forceinline__ float warp_column_sums(float* v, int lane) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-    const bool up = (lane & off) != 0;
-#pragma unroll
-    for (int i = 0; i < off; ++i) {
-      const float send = up ? v[i] : v[i + off];
-      const float keep = up ? v[i + off] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-  }
-  return v[0];
-}
-
 __global__ void __launch_bounds__(WIDE_THREADS, 1)
 grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g) {
   using G = WideGeom;
