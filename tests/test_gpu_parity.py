@@ -418,3 +418,37 @@ def test_multistep_launch_matches_per_step_launches(built, monkeypatch):
                       t_multi["momenta"], t_multi["log_u"])
     clear = np.abs(ref["log_acpt"] - t_multi["log_u"]) > 0.05
     assert np.array_equal(ref["accepted"][clear], t_multi["accepted"][clear])
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_ragged_sizes_sweep(built, prec):
+    """Seeded sweep over window counts and ragged row counts (tile edges, fewer tiles than CTAs, more
+    windows than fit one launch slot each): the batched per-call gradient of every window against the
+    oracle, the free partition (slices = 0) against a fixed one, and two short chains for determinism."""
+    m, O = built
+    rng = np.random.default_rng(20241)
+    model = O.baseline_model(tf32=bool(prec))
+    tol = TOL[prec]
+    cases = [(1, 1), (2, 127), (3, 128), (2, 129), (5, 383), (7, 385), (4, 1027), (9, 2049), (160, 200)]
+    cases += [(int(rng.integers(1, 7)), int(rng.integers(1, 6000))) for _ in range(6)]
+    for W, rows in cases:
+        data = [m.synth_window(13, g, rows) for g in range(W)]
+        w = _w(rows + W)
+        outs = []
+        for slices in (0, 3):
+            ctx = m.Context(m.baseline_config(precision=prec, slices=slices, sample_capacity=3), n_windows=W,
+                            rows=rows)
+            for i, (x, y, _) in enumerate(data):
+                ctx.set_window_data(i, x, y, global_window=i)
+            got = [ctx.potential_and_grad(i, w) for i in (0, W - 1)]
+            ctx.run_chain(3)
+            outs.append((got, ctx.get_samples(W - 1).copy()))
+            ctx.run_chain(0)
+            ctx.close()
+        for i, widx in enumerate((0, W - 1)):
+            ref = O.logp_grad(model, data[widx][0], data[widx][1], w)
+            for got, _ in outs:
+                assert _grad_err(got[i]["grad"], ref["grad"]) < tol, (W, rows)
+                assert abs(got[i]["loglik"] - ref["loglik"]) <= tol * abs(ref["loglik"]) + 1e-6, (W, rows)
+        # the partition changes the summation order only
+        assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4 * max(1e-3, np.abs(outs[1][1]).max()), (W, rows)
