@@ -1,7 +1,8 @@
 """Row sharding of one window over two GPUs (one process per GPU, NCCL
 all-reduce of the gradient partials each leapfrog step) gives the chain the
 unsharded window gives.  Needs two GPUs; NVLS is switched off for the children
-(a rank leaving while bound to a multicast object has faulted other GPUs here)."""
+(a rank that leaves while its memory is bound to an in-switch reduction group can fault
+the other ranks' GPUs)."""
 import os
 import subprocess
 import sys
