@@ -255,7 +255,7 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   if (cfg->D != 22) return fail(MCMC_B200_ERR_UNSUPPORTED, "only D = 22 is built");
   if (cfg->H != 40 && cfg->H != 128) return fail(MCMC_B200_ERR_UNSUPPORTED, "only H = 40 or 128 is built");
   if (cfg->precision == MCMC_B200_PREC_TF32 && !tf32_supported(cfg->H))
-    return fail(MCMC_B200_ERR_UNSUPPORTED, "TF32 path is built for H = 40 only");
+    return fail(MCMC_B200_ERR_UNSUPPORTED, "the TF32 path is not built for this hidden width");
   if (cfg->leapfrog_steps < 1 || cfg->lik_scale <= 0 || cfg->prior_scale <= 0)
     return fail(MCMC_B200_ERR_INVALID, "bad sampler/model constants");
   if (n_windows > 65535) return fail(MCMC_B200_ERR_INVALID, "at most 65535 windows per context");
@@ -412,21 +412,48 @@ static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_w
       }
     }
   } else {
-    G = std::max<long long>(1, std::min<long long>(max_ctas, T));
-    seg_ptr.assign(G + 1, 0);
-    for (long long b = 0; b < G; ++b) {
-      long long s = b * T / G;
-      const long long e = (b + 1) * T / G;
-      seg_ptr[b] = (int)segs.size();
-      while (s < e) {
-        const long long w = s / tiles_per_window;
-        const long long wend = std::min(e, (w + 1) * tiles_per_window);
-        segs.push_back(make_int4((int)w, (int)(s - w * tiles_per_window), (int)(wend - w * tiles_per_window),
-                                 nslot[w]++));
-        s = wend;
+    // Contiguous ranges of the flattened (window, tile) list, balanced by COST rather than by tile
+    // count: every segment a CTA starts (a new window inside its range) costs a fixed prologue + drain +
+    // read-out, worth about `seg_cost` tiles.  A CTA whose range crosses a window boundary therefore
+    // gets fewer tiles than one that stays inside a window.  The smallest per-CTA budget that covers
+    // all tiles with at most max_ctas CTAs is found by bisection over a greedy walk.
+    double seg_cost = 8.0;  // measured: 25-window step 0.656 (0) -> 0.621 (6) -> 0.619 ms (9); 200 windows 3.884 -> 3.857
+    if (const char* e = getenv("MCMC_B200_SEG_COST")) seg_cost = atof(e);
+    const long long tpw = tiles_per_window;
+    const long long Gmax = std::max<long long>(1, std::min<long long>(max_ctas, T));
+    auto walk = [&](double budget_per_cta, bool emit) -> long long {
+      long long pos = 0, used = 0;
+      while (pos < T) {
+        if (emit) seg_ptr.push_back((int)segs.size());
+        double budget = budget_per_cta;
+        bool first = true;
+        while (pos < T) {
+          long long can = (long long)std::floor(budget - seg_cost + 1e-9);
+          if (can < 1) {
+            if (!first) break;
+            can = 1;  // a CTA always takes at least one tile
+          }
+          const long long w = pos / tpw;
+          const long long take = std::min(can, (w + 1) * tpw - pos);
+          if (emit)
+            segs.push_back(make_int4((int)w, (int)(pos - w * tpw), (int)(pos + take - w * tpw), nslot[w]++));
+          pos += take;
+          budget -= seg_cost + (double)take;
+          first = false;
+        }
+        if (++used > 4 * Gmax + 16) break;  // cannot happen for a budget >= the lower bound
       }
+      return used;
+    };
+    double lo = (double)T / (double)Gmax, hi = (double)T / (double)Gmax + seg_cost * ((double)(T / Gmax) / tpw + 3.0) + 2.0;
+    while (walk(hi, false) > Gmax) hi *= 1.5;
+    for (int it = 0; it < 48; ++it) {
+      const double mid = 0.5 * (lo + hi);
+      if (walk(mid, false) <= Gmax) hi = mid; else lo = mid;
     }
+    G = walk(hi, true);
   }
+  seg_ptr.resize(G + 1);
   seg_ptr[G] = (int)segs.size();
   int ms = 1;
   for (int w = 0; w < windows; ++w) ms = std::max(ms, nslot[w]);
