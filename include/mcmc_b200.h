@@ -177,6 +177,23 @@ int mcmc_b200_final_loss(mcmc_b200_ctx* ctx, int window, int first, int count, d
                          double* mean_logprior);
 
 /*
+ * Work partition of the persistent TF32 kernels, for inspection and tests (host
+ * arithmetic only, needs no GPU).  A launch covers `windows` windows of
+ * `tiles_per_window` 128-row tiles with at most max_ctas CTAs; CTA b owns the
+ * segments seg_ptr[b] .. seg_ptr[b+1]-1, a segment is {window, first tile, end
+ * tile, slot} (slot = index of this CTA's partial-gradient vector within the
+ * window).  slices = 0: contiguous ranges balanced by cost (tiles plus a fixed
+ * cost per segment); slices > 0: every window cut into that many fixed chunks
+ * (results then do not depend on what else shares the launch).  The reference's
+ * counterpart is the compile-time N_BLKS / N_WARP_SAMPLES grid arithmetic
+ * (mcmc_step_ffma.h:40-52, mcmc_step_tc.h:145-155).  Either output array may be
+ * null to query the counts only.
+ */
+int mcmc_b200_plan_work_table(int windows, int64_t tiles_per_window, int max_ctas, int slices,
+                              int32_t* seg_ptr_out, int seg_ptr_capacity, int32_t* segs_out,
+                              int segs_capacity, int32_t* n_ctas, int32_t* n_segs);
+
+/*
  * Dataset text reader: the layout the reference's read_data scans
  * (io.h:42-80, sizes in global_params.h:61-65 there).  Whitespace-separated
  * tokens: total_cols header tokens (ignored), then `rows` rows of total_cols

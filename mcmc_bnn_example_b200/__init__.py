@@ -39,7 +39,7 @@ EXPORTS = [
     "mcmc_b200_log_acpt", "mcmc_b200_synth_window", "mcmc_b200_philox_normal", "mcmc_b200_philox_raw",
     "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
     "mcmc_b200_checkpoint_size", "mcmc_b200_checkpoint_save", "mcmc_b200_checkpoint_load",
-    "mcmc_b200_read_table",
+    "mcmc_b200_read_table", "mcmc_b200_plan_work_table",
 ]
 
 
@@ -168,6 +168,21 @@ def read_table(path, rows, total_cols=149, skip_cols=2, D=22, feature_scale=0.00
     _check(lib().mcmc_b200_read_table(os.fsencode(path), C.c_int64(rows), total_cols, skip_cols, D,
                                       C.c_float(feature_scale), _fp(x), _fp(y)))
     return x, y
+
+
+def plan_work_table(windows, tiles_per_window, max_ctas=148, slices=0):
+    """The persistent kernels' work partition: list (one entry per CTA) of lists of
+    (window, first_tile, end_tile, slot).  Host arithmetic only."""
+    n_ctas, n_segs = C.c_int32(), C.c_int32()
+    _check(lib().mcmc_b200_plan_work_table(windows, C.c_int64(tiles_per_window), max_ctas, slices, None, 0,
+                                           None, 0, C.byref(n_ctas), C.byref(n_segs)))
+    sp = np.empty(n_ctas.value + 1, np.int32)
+    sg = np.empty((n_segs.value, 4), np.int32)
+    _check(lib().mcmc_b200_plan_work_table(windows, C.c_int64(tiles_per_window), max_ctas, slices,
+                                           sp.ctypes.data_as(C.POINTER(C.c_int32)), sp.size,
+                                           sg.ctypes.data_as(C.POINTER(C.c_int32)), n_segs.value,
+                                           C.byref(n_ctas), C.byref(n_segs)))
+    return [[tuple(int(v) for v in sg[i]) for i in range(sp[b], sp[b + 1])] for b in range(n_ctas.value)]
 
 
 def nccl_unique_id():

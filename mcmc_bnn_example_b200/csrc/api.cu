@@ -390,12 +390,14 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   return MCMC_B200_OK;
 }
 
-static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
-                            int chunks_per_window, int** d_seg_ptr, int4** d_segs, int** d_nslot,
-                            int* n_ctas, int* max_slots) {
+// Host-only planner of the persistent kernels' work table: which (window, tile range, slot) segments each
+// CTA owns.  Pure arithmetic (no CUDA): also exported for inspection and CPU tests.
+static void plan_work_table(int windows, long long tiles_per_window, int max_ctas, int chunks_per_window,
+                            std::vector<int>& seg_ptr, std::vector<int4>& segs, std::vector<int>& nslot) {
   const long long T = (long long)windows * tiles_per_window;
-  std::vector<int> seg_ptr, nslot(windows, 0);
-  std::vector<int4> segs;
+  seg_ptr.clear();
+  segs.clear();
+  nslot.assign(windows, 0);
   long long G;
   if (chunks_per_window > 0) {
     long long cpw = std::min<long long>(std::min<long long>(chunks_per_window, tiles_per_window), MAX_SLICES);
@@ -455,6 +457,15 @@ static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_w
   }
   seg_ptr.resize(G + 1);
   seg_ptr[G] = (int)segs.size();
+}
+
+static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_window, int max_ctas,
+                            int chunks_per_window, int** d_seg_ptr, int4** d_segs, int** d_nslot,
+                            int* n_ctas, int* max_slots) {
+  std::vector<int> seg_ptr, nslot;
+  std::vector<int4> segs;
+  plan_work_table(windows, tiles_per_window, max_ctas, chunks_per_window, seg_ptr, segs, nslot);
+  const long long G = (long long)seg_ptr.size() - 1;
   int ms = 1;
   for (int w = 0; w < windows; ++w) ms = std::max(ms, nslot[w]);
   int r = dalloc(c, (void**)d_seg_ptr, seg_ptr.size() * sizeof(int), false);
@@ -466,6 +477,32 @@ static int build_work_table(mcmc_b200_ctx* c, int windows, long long tiles_per_w
   CK(cudaMemcpy(*d_nslot, nslot.data(), nslot.size() * sizeof(int), cudaMemcpyHostToDevice));
   *n_ctas = (int)G;
   *max_slots = ms;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_plan_work_table(int windows, int64_t tiles_per_window, int max_ctas, int slices,
+                                  int32_t* seg_ptr_out, int seg_ptr_capacity, int32_t* segs_out,
+                                  int segs_capacity, int32_t* n_ctas, int32_t* n_segs) {
+  if (windows < 1 || tiles_per_window < 1 || max_ctas < 1 || slices < 0 || !n_ctas || !n_segs)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  std::vector<int> seg_ptr, nslot;
+  std::vector<int4> segs;
+  plan_work_table(windows, tiles_per_window, max_ctas, slices, seg_ptr, segs, nslot);
+  *n_ctas = (int32_t)seg_ptr.size() - 1;
+  *n_segs = (int32_t)segs.size();
+  if (seg_ptr_out) {
+    if ((int)seg_ptr.size() > seg_ptr_capacity) return fail(MCMC_B200_ERR_INVALID, "seg_ptr_out too small");
+    for (size_t i = 0; i < seg_ptr.size(); ++i) seg_ptr_out[i] = seg_ptr[i];
+  }
+  if (segs_out) {
+    if ((int)segs.size() > segs_capacity) return fail(MCMC_B200_ERR_INVALID, "segs_out too small");
+    for (size_t i = 0; i < segs.size(); ++i) {
+      segs_out[4 * i] = segs[i].x;
+      segs_out[4 * i + 1] = segs[i].y;
+      segs_out[4 * i + 2] = segs[i].z;
+      segs_out[4 * i + 3] = segs[i].w;
+    }
+  }
   return MCMC_B200_OK;
 }
 

@@ -116,3 +116,44 @@ def test_read_table_matches_a_plain_parse(tmp_path):
         m.read_table(str(path), rows + 1)
     with pytest.raises(m.McmcError, match="cannot open"):
         m.read_table(str(tmp_path / "nope.txt"), 1)
+
+
+@pytest.mark.parametrize("slices", [0, 3])
+def test_work_partition_covers_every_tile_once_and_is_balanced(slices):
+    """The persistent kernels' work table (host arithmetic): every (window, tile) is owned by exactly one
+    CTA, a CTA's segments are contiguous in the flattened order, slots number a window's pieces 0..k-1,
+    and with the free partition no CTA costs more than equal tile counts would cost the worst CTA."""
+    import mcmc_bnn_example_b200 as m
+    m.build()
+    seg_cost = 8.0
+    for W, tpw, G in [(1, 456, 148), (25, 456, 148), (200, 456, 148), (64, 8192, 148), (3, 24, 148), (7, 3, 148),
+                      (5, 1, 148), (148, 1, 148), (149, 2, 148), (2, 1000, 7)]:
+        plan = m.plan_work_table(W, tpw, G, slices)
+        assert 1 <= len(plan) <= G
+        owned = np.zeros((W, tpw), np.int32)
+        slots = [[] for _ in range(W)]
+        costs = []
+        flat_pos = 0
+        for cta in plan:
+            assert cta, "a CTA of the table owns at least one segment"
+            tiles = 0
+            for (w, t0, t1, slot) in cta:
+                assert 0 <= w < W and 0 <= t0 < t1 <= tpw
+                owned[w, t0:t1] += 1
+                slots[w].append(slot)
+                tiles += t1 - t0
+                if slices == 0:  # contiguous in the flattened (window, tile) order
+                    assert w * tpw + t0 == flat_pos
+                    flat_pos = w * tpw + t1
+            costs.append(tiles + seg_cost * len(cta))
+        assert np.all(owned == 1)
+        for w in range(W):
+            assert sorted(slots[w]) == list(range(len(slots[w])))
+            if slices:
+                assert len(slots[w]) == min(slices, tpw)
+        if slices == 0:
+            T = W * tpw
+            n = min(G, T)
+            even_tiles = -(-T // n)
+            worst_segments = (even_tiles + tpw - 2) // tpw + 1  # windows an even range can touch
+            assert max(costs) <= even_tiles + seg_cost * worst_segments + 1e-9
