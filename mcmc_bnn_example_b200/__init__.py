@@ -72,8 +72,6 @@ def build(force=False, verbose=False):
            "-o", LIB_PATH] + src + ["-ldl"]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
-    if os.environ.get("MCMC_B200_EXPERIMENTS"):
-        cmd.insert(1, "-DMCMC_B200_EXPERIMENTS")  # ablation / phase-timing hooks in the TF32 kernel
     subprocess.check_call(cmd)
     return LIB_PATH
 
@@ -382,8 +380,3 @@ class Context:
         s, c, t = C.c_int(), C.c_int(), C.c_int()
         _check(lib().mcmc_b200_chain_geometry(self._h, C.byref(s), C.byref(c), C.byref(t)))
         return dict(slices=s.value, ctas_per_sm=c.value, tile_rows=t.value)
-
-    def debug_dump(self, n=12288):
-        out = np.empty(n, np.float32)
-        _check(lib().mcmc_b200_debug_dump(self._h, _fp(out), n))
-        return out

@@ -140,7 +140,6 @@ struct mcmc_b200_ctx {
   // all L leapfrog steps of an iteration in one cooperative launch (one window, TF32, H = 40)
   bool multistep = false;
   unsigned int* grid_bar = nullptr;
-  float* dbg = nullptr;
   float* stage = nullptr;  // upload staging for one window: [rows][D] then [rows]
   std::vector<void*> allocs;
 };
@@ -367,7 +366,6 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   DA(c->row_loss, (size_t)c->rows_pad * 4);
   DA(c->scalars, 4 * 8);
   DA(c->scalar_f, 16);
-  DA(c->dbg, 16384 * 4);
   if (cfg->sample_capacity > 0) {
     int r_ = dalloc(c, (void**)&c->samples, W * (size_t)cfg->sample_capacity * P * 4, false);
     if (r_ != MCMC_B200_OK) { mcmc_b200_destroy(c); return r_; }
@@ -419,8 +417,7 @@ static void plan_work_table(int windows, long long tiles_per_window, int max_cta
     // read-out, worth about `seg_cost` tiles.  A CTA whose range crosses a window boundary therefore
     // gets fewer tiles than one that stays inside a window.  The smallest per-CTA budget that covers
     // all tiles with at most max_ctas CTAs is found by bisection over a greedy walk.
-    double seg_cost = 8.0;  // measured: 25-window step 0.656 (0) -> 0.621 (6) -> 0.619 ms (9); 200 windows 3.884 -> 3.857
-    if (const char* e = getenv("MCMC_B200_SEG_COST")) seg_cost = atof(e);
+    const double seg_cost = 8.0;  // measured: 25-window step 0.656 (0) -> 0.621 (6) -> 0.619 ms (9); 200 windows 3.884 -> 3.857
     const long long tpw = tiles_per_window;
     const long long Gmax = std::max<long long>(1, std::min<long long>(max_ctas, T));
     auto walk = [&](double budget_per_cta, bool emit) -> long long {
@@ -580,12 +577,11 @@ static GradParams base_grad_params(mcmc_b200_ctx* c) {
   g.lik = make_lik(c->cfg);
   g.prior = make_prior(c->cfg);
   g.status = c->status;
-  { const char* a = getenv("MCMC_B200_ABLATE"); g.ablate = a ? atoi(a) : 0; }
   return g;
 }
 
 // `single` selects the single-window work table / slot count (explicit-state calls)
-static int launch_grad(mcmc_b200_ctx* c, GradParams g, bool single, cudaStream_t st, float* dbg = nullptr) {
+static int launch_grad(mcmc_b200_ctx* c, GradParams g, bool single, cudaStream_t st) {
   cudaError_t e;
   const int slots = single ? c->slices_x : c->slices;
   g.slices_in = slots;
@@ -594,7 +590,7 @@ static int launch_grad(mcmc_b200_ctx* c, GradParams g, bool single, cudaStream_t
     g.nslot_in = single ? c->xtab_nslot : c->tab_nslot;
     g.seg_ptr = single ? c->xtab_seg_ptr : c->tab_seg_ptr;
     g.segs = single ? c->xtab_segs : c->tab_segs;
-    e = launch_grad_tf32(c->cfg.H, &c->tmap_mn, g, single ? c->xtab_ctas : c->tab_ctas, dbg, st);
+    e = launch_grad_tf32(c->cfg.H, &c->tmap_mn, g, single ? c->xtab_ctas : c->tab_ctas, st);
   } else {
     e = launch_grad_fp32(c->cfg.H, g, slots, single ? 1 : c->W, st);
   }
@@ -672,7 +668,7 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   g.partial_out = c->partial[s & 1];
   g.ll_out = c->llp[s & 1];
   g.eps = c->eps;
-  int r = launch_grad(c, g, false, st, (g.ablate & 512) ? c->dbg : nullptr);
+  int r = launch_grad(c, g, false, st);
   if (r) return r;
   if (red) {
     cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->tab_nslot, c->P,
@@ -1008,7 +1004,7 @@ static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, c
     g.eps_scalar = eps;
     g.row_loss = last ? row_loss : nullptr;
     g.row_loss_stride = 0;
-    int r = launch_grad(c, g, true, st, (eval_only && c->cfg.precision == MCMC_B200_PREC_TF32) ? c->dbg : nullptr);
+    int r = launch_grad(c, g, true, st);
     if (r) return r;
     if (red) {
       cudaError_t e = launch_reduce_partials(c->xpartial[s & 1], c->xllp[s & 1], S, c->xtab_nslot, c->P, c->Pp,
@@ -1215,16 +1211,5 @@ API int mcmc_b200_chain_geometry(mcmc_b200_ctx* c, int* slices, int* ctas_per_sm
   if (slices) *slices = c->slices;
   if (ctas_per_sm) *ctas_per_sm = c->ctas_per_sm;
   if (tile_rows) *tile_rows = c->tile_rows;
-  return MCMC_B200_OK;
-}
-
-// debugging aid for the tensor-core path: first-tile pre-activations and the raw
-// backward accumulator of CTA (0,0) of the last potential_and_grad call
-extern "C" __attribute__((visibility("default"))) int mcmc_b200_debug_dump(mcmc_b200_ctx* c, float* out,
-                                                                             int n_floats) {
-  if (!c || !out || n_floats > 16384) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
-  CK(cudaSetDevice(c->device));
-  CK(cudaStreamSynchronize(c->stream));
-  CK(cudaMemcpy(out, c->dbg, (size_t)n_floats * 4, cudaMemcpyDeviceToHost));
   return MCMC_B200_OK;
 }

@@ -71,8 +71,7 @@ int fp32_tile_rows(int H);
 
 // TF32 (tcgen05) path: persistent, one CTA per SM; `tmap_mn` is a CUtensorMap over the repacked
 // dataset that stages a row tile with the 32-byte-chunk swizzle
-cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
-                             cudaStream_t st);
+cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, cudaStream_t st);
 int tf32_supported(int H);
 int tf32_multistep_max_ctas(int H);
 cudaError_t launch_grad_tf32_multistep(int H, const void* tmap_mn, const GradParams& g, int ctas,

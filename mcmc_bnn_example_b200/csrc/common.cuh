@@ -71,7 +71,8 @@ struct GradParams {
   LikParams lik;
   PriorParams prior;
   int* status;              // device error word (bounded waits that ran out)
-  int ablate;               // experiments only: bit mask of pipeline parts to skip (0 in production)
+  int data_fresh;           // 1: xaug was written by the launch directly before this one in the stream, so
+                            // no row may be fetched ahead of the programmatic-dependency wait
   // several leapfrog steps in one cooperative launch (one window; grad_tf32.cu).  Step s reads
   // w_buf/m_buf[s & 1], writes [(s + 1) & 1] and partial_buf/ll_buf[s & 1]; `red` receives the summed
   // gradient after every step; grid_bar is a zeroed arrival counter
@@ -220,11 +221,13 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
   return ok != 0;
 }
 // Bounded wait: the thread sleeps in hardware on the barrier in slices of 20 us and gives up after
-// 2^16 slices (about 1.3 s), records the code in the status word and returns false; the kernel then
-// finishes with whatever it has, so a lost copy or MMA can never hang the GPU.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+// `slices` of them (default 2^16, about 1.3 s), records the code in the status word and returns false;
+// the kernel then finishes with whatever it has, so a lost copy or MMA can never hang the GPU.
+constexpr uint32_t MBAR_WAIT_SLICES = 1u << 16;
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          uint32_t slices = MBAR_WAIT_SLICES) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t i = 0; i < (1u << 16); ++i) {
+  for (uint32_t i = 0; i < slices; ++i) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   }
   if (status) atomicExch(status, code);

@@ -110,12 +110,19 @@ __global__ void __launch_bounds__(NT, MINB) grad_fp32_kernel(const GradParams g)
     mbar_fence_init();
   }
   __syncthreads();
-  if (tid == 0 && t0 < t1) {  // the dataset is not written by any kernel of the chain
+  // The first row tile may be fetched ahead of the dependency wait only when no kernel directly before
+  // this one in the stream wrote the dataset (inside a chain none does; right after a repack one did).
+  const bool early_rows = g.data_fresh == 0;
+  if (tid == 0 && t0 < t1 && early_rows) {
     mbar_expect_tx(&bars[0], TILE_BYTES);
     bulk_g2s(xs, xw + (size_t)t0 * TILE * KP, TILE_BYTES, &bars[0]);
   }
   pdl_trigger();
   pdl_wait();
+  if (tid == 0 && t0 < t1 && !early_rows) {
+    mbar_expect_tx(&bars[0], TILE_BYTES);
+    bulk_g2s(xs, xw + (size_t)t0 * TILE * KP, TILE_BYTES, &bars[0]);
+  }
   // fused leapfrog update; parameters land in the layout the lanes read
   for (int p = tid; p < G::P; p += NT) {
     const float w = leapfrog_param(g, win, p, slice == 0);

@@ -22,16 +22,29 @@
 //             so tanh, the output layer, the loss and dZ need no cross-lane
 //             traffic (the reference reduces and broadcasts across lanes,
 //             mcmc_step_tc.h:426-432, :468-474).
-//   backward  G[64 hidden x 24] += E^T[64 x 128 rows] . Xa[128 x 24]
-//             E = (1 - h^2) * dL/dpred, written row-per-thread into shared
-//             memory as the MN-major A operand; the TMA-staged row tile is the
-//             MN-major B operand.  MN-major operands of a 32-bit type exist in
-//             one layout only, the 128-byte swizzle of 32-byte chunks, so the
-//             tile is staged in that layout (and that is why the forward takes
-//             its A operand from tensor memory instead of a second copy of the
-//             tile).  G stays in tensor memory for a whole segment and is read
-//             once: dW0[k][j] = W1[j] * G[j][k], db0[j] = W1[j] * G[j][22] — W1[j]
-//             is a per-output-row constant, applied after the reduction.
+//   backward  Gt[feature x hidden] += Xa^T[feature x rows] . E[rows x hidden]
+//             E = (1 - h^2) * dL/dpred (stored negated, see below), written
+//             row-per-thread into shared memory as the K-major B operand (one
+//             128-byte line per hidden unit and 32 rows); the TMA-staged row
+//             tile is the MN-major A operand.  MN-major operands of a 32-bit
+//             type exist in one layout only, the 128-byte swizzle of 32-byte
+//             chunks, so the tile is staged in that layout (and that is why the
+//             forward takes its A operand from tensor memory instead of a
+//             second copy of the tile).
+//             The cost of a tcgen05.mma of this size is its issue, not its
+//             arithmetic, and K is fixed at 8 rows per instruction.  One
+//             instruction therefore covers TWO 32-row groups at once: M = 64 =
+//             the 32-float rows of group a and of group a+1 (the second
+//             32-float atom of the MN-major operand is simply the tile 32 rows
+//             further down), N = 80 = the 40 lines of E for group a followed by
+//             the 40 lines for group a+1.  The two diagonal blocks of the
+//             64 x 80 result are the wanted sums, the off-diagonal blocks
+//             (group a's rows against group a+1's E) are never read: 8
+//             instructions per 128-row tile instead of 16, and no line of E is
+//             fetched that is not used.  Gt stays in tensor memory for a whole
+//             segment and is read once: dW0[k][j] = W1[j] * Gt[k][j],
+//             db0[j] = W1[j] * Gt[22][j] — W1[j] is a per-column constant,
+//             applied after the reduction.
 //
 // TF32 semantics: operands are raw FP32 bit patterns whose low 13 mantissa
 // bits the tensor core ignores, as in the reference (mov.b32 of FP32 values,
@@ -61,25 +74,24 @@ template <int H>
 struct Tf32Geom {
   static constexpr int D = 22;
   static constexpr int NF = (H + 15) / 16 * 16;        // forward N (M = 128 needs N % 16 == 0)
-  static constexpr int MB = 64;                        // backward M (hidden, padded)
-  static constexpr int NB = 24;                        // backward N (features + 1 + y)
+  static constexpr int GM = 64;                        // backward M: two 32-float atoms of the row tile
+  static constexpr int GN = 2 * H;                     // backward N: the hidden units of two 32-row groups
   static constexpr int TILE_BYTES = TF32_TILE * 128;   // 128 rows x 32 floats (24 real + 8 zero fill)
+  static constexpr int GROUP_BYTES = 32 * 128;         // 32 rows of the staged tile
   static constexpr int XB_BYTES = TF32_NWG * TF32_NST * TILE_BYTES;
-  // E operand, K-major: 4 atoms of 32 rows (K); in an atom hidden unit j is a 128-byte line.  Only
-  // H of the MB lines are written; the lines H..MB-1 the tensor core also reads are whatever
-  // follows (they only reach accumulator rows that are never read), so atoms are packed H lines apart.
+  // E operand, K-major: 4 atoms of 32 rows (K); in an atom hidden unit j is a 128-byte line
   static constexpr int ES_ATOM_BYTES = H * 128;
   static constexpr int ES_WG_BYTES = 4 * ES_ATOM_BYTES;
-  static constexpr int ES_BYTES = TF32_NWG * ES_WG_BYTES + (MB - H) * 128;
+  static constexpr int ES_BYTES = TF32_NWG * ES_WG_BYTES;
   static constexpr int W0S_BYTES = NF * 128;
   static constexpr int W1_BYTES = (H + 3) / 4 * 16;
   static constexpr int P = D * H + 2 * H + 1;
   static constexpr size_t SMEM = 1024 + XB_BYTES + ES_BYTES + W0S_BYTES + W1_BYTES;
-  // tensor-memory columns: A operand and forward accumulator per warpgroup, one backward accumulator
-  // (the forward accumulator is double-buffered: forward(n+1) runs while Z(n) is being consumed)
+  // tensor-memory columns per warpgroup: forward A operand, forward accumulator (one buffer: forward(n+1)
+  // is issued only after Z(n) has been read into registers), backward accumulator
   static constexpr int A_COL0 = 0, A_STRIDE = 24;
   static constexpr int Z_COL0 = TF32_NWG * A_STRIDE, Z_STRIDE = NF;
-  static constexpr int G_COL0 = Z_COL0 + 2 * TF32_NWG * Z_STRIDE, G_STRIDE = 24;
+  static constexpr int G_COL0 = Z_COL0 + TF32_NWG * Z_STRIDE, G_STRIDE = GN;
   static constexpr int TMEM_COLS = 512;
   static_assert(H % 8 == 0 && H <= 64, "hidden width must be a multiple of 8, at most 64");
   static_assert(G_COL0 + TF32_NWG * G_STRIDE <= TMEM_COLS, "tensor memory budget");
@@ -87,32 +99,24 @@ struct Tf32Geom {
   static_assert(ES_ATOM_BYTES % 1024 == 0, "E atoms must keep the 1024-byte swizzle alignment");
 };
 
-// Experiments (built only with -DMCMC_B200_EXPERIMENTS): ABL(bit) skips a part of the pipeline when
-// that bit is set in GradParams::ablate, PROF_MARK accumulates clock64 deltas per phase in thread 0 of
-// each warpgroup of CTA 0.  In the production build both vanish at compile time.
-#ifdef MCMC_B200_EXPERIMENTS
-#define ABL(bit) ((g.ablate & (bit)) != 0)
-#define PROF_DECL                                                                        \
-  const bool prof = dbg && ABL(512) && blockIdx.x == 0 && wtid == 0;             \
-  long long pacc[10] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0};                                   \
-  long long plast = clock64();
-#define PROF_MARK(k)                                   \
-  if (prof) {                                          \
-    const long long now_ = clock64();                  \
-    pacc[k] += now_ - plast;                           \
-    plast = now_;                                      \
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// The slow side of a bounded wait, out of line so that the five waits of a tile cost one test each.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+  for (uint32_t i = 0; i < MBAR_WAIT_SLICES; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   }
-#define PROF_FLUSH                                                                        \
-  if (prof) {                                                                             \
-    for (int k = 0; k < 10; ++k) dbg[12288 + wg * 16 + k] += (float)pacc[k];              \
-    dbg[12288 + wg * 16 + 10] += (float)my_nt;                                            \
-  }
-#else
-#define ABL(bit) false
-#define PROF_DECL
-#define PROF_MARK(k)
-#define PROF_FLUSH
-#endif
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ bool mbar_wait_q(uint64_t* bar, uint32_t parity, int* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, status, code);
+}
 
 // One CTA's share of the cross-CTA sum inside a multi-step launch: parameters
 // [blockIdx.x * per_cta, ...) summed over the n_slots partial vectors in a fixed order (one warp per
@@ -151,11 +155,11 @@ __device__ __forceinline__ void sum_partials_slice(const GradParams& g, const fl
 // mcmc_step_tc.h:597-677) with a bounded barrier and a fixed-order sum instead of atomics.
 template <int H, bool MULTI>
 __global__ void __launch_bounds__(TF32_THREADS, 1)
-grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g, float* dbg) {
+grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g) {
   using G = Tf32Geom<H>;
-  constexpr int D = G::D, NF = G::NF, MB = G::MB, NB = G::NB, NWG = TF32_NWG, NST = TF32_NST;
+  constexpr int D = G::D, NF = G::NF, NWG = TF32_NWG, NST = TF32_NST;
   constexpr uint32_t IDESC_FWD = umma_idesc_tf32(128, NF, 0, 0);
-  constexpr uint32_t IDESC_BWD = umma_idesc_tf32(MB, NB, 0, 1);
+  constexpr uint32_t IDESC_BWD = umma_idesc_tf32(G::GM, G::GN, 1, 0);  // A = Xa^T MN-major, B = E K-major
   constexpr int NCOMPUTE = NWG * 128;
 
   extern __shared__ unsigned char smem_raw[];
@@ -172,11 +176,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   __shared__ float red_w1[NWG * 4][H];
   __shared__ float red_db1[NWG * 4];
   __shared__ double red_ll[NWG * 4];
+  __shared__ __align__(16) float red_g[KP][H];  // the second row group's half of Gt at read-out
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const bool is_ctrl = warp >= NWG * 4;
-  const int wg = is_ctrl ? warp - NWG * 4 : warp >> 2;  // warpgroup this warp computes for / issues for
   const int wtid = tid & 127;         // row of the tile this thread owns
   const int wwarp = warp & 3;         // tensor-memory subpartition of this warp
   const int rows_pad = g.n_tiles * TF32_TILE;
@@ -219,6 +223,8 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   if (is_ctrl) {
     // =====================  control warpgroup (warps 12..15; warp 15 only keeps the barriers) ==========
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(TF32_CTRL_REGS));
+    // the warpgroup this warp issues for, in a form the compiler can see is the same in every lane
+    const int wg = __shfl_sync(0xffffffffu, warp - NWG * 4, 0);
     uint32_t c_issued = 0;  // tiles of this warpgroup whose MMAs have been issued (mbarrier phases follow it)
     bool alive = true;
     // a multi-step launch walks its segments once per step: ONE loop over (step, segment) pairs
@@ -230,23 +236,21 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       __syncthreads();  // S1
       if (wg < NWG) {
         // Order per tile n: forward(n+1) as soon as its rows are in tensor memory (the warpgroup stages
-        // them at the START of tile n), backward(n) when E(n) is in shared memory, then — once those
-        // MMAs have completed — the TMA refill of the row stage they read.
+        // them at the START of tile n, after it has read Z(n)), backward(n) when E(n) is in shared
+        // memory, then — once those MMAs have completed — the TMA refill of the row stage they read.
         const int cnt = (nt - wg + NWG - 1) / NWG;
         const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE;
-        const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE;
+        const uint32_t z_t = tmem + G::Z_COL0 + wg * G::Z_STRIDE;
         const uint32_t g_t = tmem_g + wg * G::G_STRIDE;
         // descriptors of K block 0 / row stage 0; the others differ only in the start address
         const uint64_t wdesc0 = umma_desc_k128(w0s_addr);
-        const uint64_t adesc0 = umma_desc_k128(smem_u32(es + wg * G::ES_WG_BYTES));
-        const uint64_t bdesc0 = umma_desc_mn32(smem_u32(xb + wg * NST * G::TILE_BYTES), G::TILE_BYTES);
+        const uint64_t edesc0 = umma_desc_k128(smem_u32(es + wg * G::ES_WG_BYTES));
+        const uint64_t xdesc0 = umma_desc_mn32(smem_u32(xb + wg * NST * G::TILE_BYTES), G::GROUP_BYTES);
         uint32_t stage = c_issued % NST;  // row stage of tile n, kept as a running counter
-        auto issue_fwd = [&](uint32_t n) {
+        auto issue_fwd = [&]() {
           named_sync(BAR_ROWS0 + wg, 160);
           if (lane == 0) {
             tc_fence_after();
-            const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
-            if (!ABL(32))
 #pragma unroll
             for (int kb = 0; kb < 3; ++kb)
               tc_mma_tf32_ts(z_t, a_t + kb * 8, umma_desc_advance(wdesc0, kb * 2), IDESC_FWD, kb > 0);
@@ -254,22 +258,24 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
           }
           __syncwarp();
         };
-        if (cnt > 0) issue_fwd(c_issued);
+        if (cnt > 0) issue_fwd();
         for (int i = 0; i < cnt; ++i) {
           const uint32_t n = c_issued + i;
-          if (i + 1 < cnt) issue_fwd(n + 1);
+          if (i + 1 < cnt) issue_fwd();
           named_sync(BAR_E0 + wg, 160);
           if (lane == 0) {
             tc_fence_after();
-            const uint64_t bd = umma_desc_advance(bdesc0, stage * (G::TILE_BYTES >> 4));
-            if (!ABL(1))
+            const uint64_t xd = umma_desc_advance(xdesc0, stage * (G::TILE_BYTES >> 4));
+            // pair p = row groups 2p, 2p+1 (rows 64p .. 64p+63 of the tile); K block kb = 8 rows of each group
 #pragma unroll
-            for (int kb = 0; kb < TF32_TILE / 8; ++kb)
-              tc_mma_tf32_ss(g_t,
-                             umma_desc_advance(adesc0, (kb >> 2) * (G::ES_ATOM_BYTES >> 4) + (kb & 3) * 2),
-                             umma_desc_advance(bd, kb * 64), IDESC_BWD, (i == 0 && kb == 0) ? 0u : 1u);
+            for (int q = 0; q < 8; ++q) {
+              const int p = q >> 2, kb = q & 3;
+              tc_mma_tf32_ss(g_t, umma_desc_advance(xd, p * (2 * G::GROUP_BYTES >> 4) + kb * 64),
+                             umma_desc_advance(edesc0, p * (2 * G::ES_ATOM_BYTES >> 4) + kb * 2), IDESC_BWD,
+                             (i == 0 && q == 0) ? 0u : 1u);
+            }
             tc_commit(&bar_bwd[wg]);
-            if (i + NST < cnt && !ABL(256)) {
+            if (i + NST < cnt) {
               ok = ok && mbar_wait(&bar_bwd[wg], n & 1, g.status, 213);
               if (ok) {
                 mbar_expect_tx(&bar_tma[wg][stage], G::TILE_BYTES);
@@ -294,20 +300,27 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   } else {
     // =====================  compute warpgroups: one row per thread  =====================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TF32_COMPUTE_REGS));
+    const int wg = warp >> 2;
     uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
     uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
     const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
     const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
-    const uint32_t z_t0 = tmem + G::Z_COL0 + wg * 2 * G::Z_STRIDE + lane_off;
+    const uint32_t z_t = tmem + G::Z_COL0 + wg * G::Z_STRIDE + lane_off;
     // E element (hidden j, row r): atom r/32 (= this warp), line j, 16-byte chunk (r%32)/4 ^ (j%8)
     uint32_t e_ptr[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c)
       e_ptr[c] = smem_u32(es + wg * G::ES_WG_BYTES + wwarp * G::ES_ATOM_BYTES) +
                  ((uint32_t)(((lane >> 2) ^ c) << 4)) + ((lane & 3) << 2);
-    // rows r and r+4 of a staged tile keep their 32-byte chunks in the same banks: the upper four of
-    // every eight rows read the two halves of a chunk in the opposite order
+    // This thread's row in a staged tile: 32-byte chunk j of row r sits at position j ^ (r % 4).  Rows r
+    // and r+4 keep their chunks in the same banks, so the upper four of every eight rows read the two
+    // 16-byte halves of a chunk in the opposite order (address ^ 16) and swap them back in registers.
     const bool swap_halves = (wtid & 4) != 0;
+    const uint32_t xb_wg = smem_u32(xb + wg * NST * G::TILE_BYTES);
+    uint32_t x_off[3];
+#pragma unroll
+    for (int j = 0; j < 3; ++j)
+      x_off[j] = (uint32_t)(wtid * 128 + ((j ^ (wtid & 3)) << 5) + (swap_halves ? 16 : 0));
     bool alive = true;
 
     for (int it = 0; it < n_iters; ++it) {
@@ -320,7 +333,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       const int my_nt = (nt - wg + NWG - 1) / NWG;          // tiles t0 + wg, t0 + wg + NWG, ...
 
       // ---- segment prologue: start the first row tiles, fused leapfrog update, stage W0a ----
-      if (wtid == 0 && !ABL(256)) {
+      if (wtid == 0) {
         for (int i = 0; i < NST && i < my_nt; ++i) {
           const uint32_t n = n_done + i;
           mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
@@ -363,28 +376,22 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         const uint32_t stage = st_stage, phase = st_phase;  // of the tile being staged
         st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
         st_phase ^= (st_stage == 0) ? 1u : 0u;
-        if (!ABL(256)) ok = ok && mbar_wait(&bar_tma[wg][stage], phase, g.status, 201);
-        // 32-byte chunk j of a row sits at position j ^ (row % 4)
-        const unsigned char* xrow = xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128;
-        float4 xr[6];
+        ok = ok && mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 201);
+        const uint32_t sb = xb_wg + stage * G::TILE_BYTES;
+        float yv = 0.f;
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
-          const unsigned char* cp = xrow + ((j ^ (wtid & 3)) << 5);
-          const float4 first = *reinterpret_cast<const float4*>(cp + (swap_halves ? 16 : 0));
-          const float4 second = *reinterpret_cast<const float4*>(cp + (swap_halves ? 0 : 16));
-          xr[2 * j].x = swap_halves ? second.x : first.x;
-          xr[2 * j].y = swap_halves ? second.y : first.y;
-          xr[2 * j].z = swap_halves ? second.z : first.z;
-          xr[2 * j].w = swap_halves ? second.w : first.w;
-          xr[2 * j + 1].x = swap_halves ? first.x : second.x;
-          xr[2 * j + 1].y = swap_halves ? first.y : second.y;
-          xr[2 * j + 1].z = swap_halves ? first.z : second.z;
-          xr[2 * j + 1].w = swap_halves ? first.w : second.w;
+          const uint32_t a = sb + x_off[j];
+          const float4 p = lds128(a), q = lds128(a ^ 16u);
+          float4 lo, hi;
+          lo.x = swap_halves ? q.x : p.x; lo.y = swap_halves ? q.y : p.y;
+          lo.z = swap_halves ? q.z : p.z; lo.w = swap_halves ? q.w : p.w;
+          hi.x = swap_halves ? p.x : q.x; hi.y = swap_halves ? p.y : q.y;
+          hi.z = swap_halves ? p.z : q.z; hi.w = swap_halves ? p.w : q.w;
+          tc_st8(a_t + j * 8, lo, hi);
+          if (j == 2) yv = hi.w;
         }
-        if (!ABL(64))
-#pragma unroll
-        for (int j = 0; j < 3; ++j) tc_st8(a_t + j * 8, xr[2 * j], xr[2 * j + 1]);
-        return xr[5].w;
+        return yv;
       };
       // ... and tells the control warp once the stores have landed
       auto publish_row = [&]() {
@@ -393,55 +400,34 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         named_arrive(BAR_ROWS0 + wg, 160);
       };
 
-      PROF_DECL
       float y = 0.f;
       if (my_nt > 0) {
         y = stage_row();
         publish_row();
       }
-      PROF_MARK(9)
       for (int i = 0; i < my_nt; ++i) {
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
-        ok = ok && mbar_wait(&bar_fwd[wg], n & 1, g.status, 202);
+        ok = ok && mbar_wait_q(&bar_fwd[wg], n & 1, g.status, 202);
         tc_fence_after();
-        PROF_MARK(0)
-        // forward(n) is done with the A operand: the next tile's rows go in now, so that forward(n+1)
-        // (into the other accumulator buffer) has this whole tile's epilogue to complete
+        // forward(n) is done with the A operand: the next tile's rows go in now, and once Z(n) is in
+        // registers forward(n+1) may overwrite the accumulator: it has this whole tile's epilogue to complete
         float y_next = 0.f;
         if (i + 1 < my_nt) y_next = stage_row();
-        PROF_MARK(1)
-        const uint32_t z_t = z_t0 + (n & 1) * G::Z_STRIDE;
         float z[H];
-        if (!ABL(128)) {
 #pragma unroll
-          for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
-          tc_wait_ld();
-        } else {
-#pragma unroll
-          for (int c = 0; c < H; ++c) z[c] = 0.01f * c;
-        }
-        PROF_MARK(2)
+        for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
+        tc_wait_ld();
         if (i + 1 < my_nt) publish_row();
-        PROF_MARK(3)
-        if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0 && wg == 0 && i == 0) {
+        float pred = b1, pred1 = 0.f;
 #pragma unroll
-          for (int j = 0; j < H; ++j) dbg[wtid * 64 + j] = z[j];
-          dbg[wtid * 64 + 63] = y;
+        for (int j = 0; j < H; j += 2) {
+          z[j] = tanh_fast(z[j]);
+          z[j + 1] = tanh_fast(z[j + 1]);
+          pred = fmaf(w1r[j], z[j], pred);
+          pred1 = fmaf(w1r[j + 1], z[j + 1], pred1);
         }
-        float pred = b1;
-        if (!ABL(8)) {
-          float pred1 = 0.f;
-#pragma unroll
-          for (int j = 0; j < H; j += 2) {
-            z[j] = tanh_fast(z[j]);
-            z[j + 1] = tanh_fast(z[j + 1]);
-            pred = fmaf(w1r[j], z[j], pred);
-            pred1 = fmaf(w1r[j + 1], z[j + 1], pred1);
-          }
-          pred += pred1;
-        }
-        PROF_MARK(4)
+        pred += pred1;
         const int grow = t * TF32_TILE + wtid;
         const bool valid = grow < g.n_rows;
         float loss, dy;
@@ -450,32 +436,29 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         llacc += (double)loss;
         if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
         db1 += dy;
-        if (!ABL(16)) {
-          const uint64_t dy2 = pack2(dy, dy), one2 = pack2(1.f, 1.f);
+        {
+          // with t = dy*h:  dW1 += t,  -E = t*h - dy  (E = (1 - h^2) dy; the sign and the W1 factor are
+          // applied once per segment at read-out): three packed operations per pair of hidden units
+          const uint64_t dy2 = pack2(dy, dy), ndy2 = pack2(-dy, -dy);
 #pragma unroll
           for (int j = 0; j < H; j += 2) {
             const uint64_t h2 = pack2(z[j], z[j + 1]);
-            const uint64_t nh2 = pack2(-z[j], -z[j + 1]);
+            const uint64_t t2 = mul2(dy2, h2);
             dw1p[j >> 1] = fma2(dy2, h2, dw1p[j >> 1]);
-            const uint64_t e2 = mul2(fma2(nh2, h2, one2), dy2);  // E; the W1 factor is applied at read-out
-            unpack2(e2, z[j], z[j + 1]);
+            unpack2(fma2(t2, h2, ndy2), z[j], z[j + 1]);
           }
         }
-        PROF_MARK(5)
         // the previous tile's backward MMAs must be done with E before it is overwritten
-        if (n > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n - 1) & 1, g.status, 203);
-        PROF_MARK(6)
-        if (!ABL(4)) store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
+        if (n > 0) ok = ok && mbar_wait_q(&bar_bwd[wg], (n - 1) & 1, g.status, 203);
+        store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
         fence_proxy_async_smem();
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
-        PROF_MARK(7)
       }
-      PROF_FLUSH
       n_done += my_nt;
 
       // ---- this warp's share of dW1 / db1 / log-lik ----
-      if (n_done > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n_done - 1) & 1, g.status, 204);
+      if (n_done > 0) ok = ok && mbar_wait_q(&bar_bwd[wg], (n_done - 1) & 1, g.status, 204);
       tc_fence_after();
       {
         // column sums over the warp's 32 rows: a halving butterfly leaves hidden unit `lane` in lane `lane`
@@ -516,35 +499,46 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       // ---- segment read-out: one partial gradient vector for (window, slot) ----
       float* po = (MULTI ? ((step & 1) ? g.partial_buf[1] : g.partial_buf[0]) : g.partial_out) + ((size_t)win * g.slices_out + slot) * g.Pp;
       if (warp < 4) {
+        // Gt accumulator row i = 32 * group + feature lives in lane 32 * (i / 16) + i % 16 (M = 64): warp w
+        // holds, in its lanes 0..15, features 16 * (w & 1) + lane of row group w >> 1, whose hidden
+        // units are columns H * (w >> 1) .. + H - 1
         tc_fence_after();
-        float gacc[NB];
-        const uint32_t trow = tmem_g + ((uint32_t)(warp * 32) << 16);
+        const int grp = warp >> 1, k = (warp & 1) * 16 + lane;
+        const uint32_t trow = tmem_g + ((uint32_t)(warp * 32) << 16) + grp * H;
+        float gacc[H];
 #pragma unroll
-        for (int c = 0; c < NB; c += 8) tc_ld8(trow + c, gacc + c);
+        for (int c = 0; c < H; c += 8) tc_ld8(trow + c, gacc + c);
         tc_wait_ld();
         // the other warpgroups' accumulators (those that had tiles in this segment)
 #pragma unroll
         for (int w = 1; w < NWG; ++w) {
           if (w < nt) {
-            float g2[NB];
+            float g2[H];
 #pragma unroll
-            for (int c = 0; c < NB; c += 8) tc_ld8(trow + w * G::G_STRIDE + c, g2 + c);
+            for (int c = 0; c < H; c += 8) tc_ld8(trow + w * G::G_STRIDE + c, g2 + c);
             tc_wait_ld();
 #pragma unroll
-            for (int c = 0; c < NB; ++c) gacc[c] += g2[c];
+            for (int c = 0; c < H; ++c) gacc[c] += g2[c];
           }
         }
-        if (dbg && !ABL(512) && blockIdx.x == 0 && sg == seg0) {
+        const bool mine = lane < 16 && k <= COL_ONE;  // feature rows 0..21 and the constant-1 row (db0)
+        if (grp == 1 && mine) {
 #pragma unroll
-          for (int c = 0; c < NB; ++c) dbg[8192 + tid * 32 + c] = gacc[c];
+          for (int c = 0; c < H; c += 4)
+            *reinterpret_cast<float4*>(&red_g[k][c]) = make_float4(gacc[c], gacc[c + 1], gacc[c + 2], gacc[c + 3]);
         }
-        // M = 64: accumulator row i lives in lane 32*(i/16) + i%16
-        const int hidx = lane < 16 ? warp * 16 + lane : -1;
-        if (hidx >= 0 && hidx < H) {
-          const float w1 = w1s[hidx];
+        named_sync(1, 128);
+        if (grp == 0 && mine) {
+          // dW0[k][j] = W1[j] * Gt[k][j]; E was stored negated
+          float* dst = po + k * H;
 #pragma unroll
-          for (int k = 0; k < D; ++k) po[k * H + hidx] = w1 * gacc[k];
-          po[D * H + hidx] = w1 * gacc[COL_ONE];
+          for (int c = 0; c < H; c += 4) {
+            const float4 o = *reinterpret_cast<const float4*>(&red_g[k][c]);
+            const float4 w1 = *reinterpret_cast<const float4*>(w1s + c);
+            *reinterpret_cast<float4*>(dst + c) =
+                make_float4(-w1.x * (gacc[c] + o.x), -w1.y * (gacc[c + 1] + o.y),
+                            -w1.z * (gacc[c + 2] + o.z), -w1.w * (gacc[c + 3] + o.w));
+          }
         }
         tc_fence_before();
       } else if (warp == 4) {
@@ -587,8 +581,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
 int tf32_supported(int H) { return H == 40 || H == 128; }
 
 template <int H>
-static cudaError_t launch_tf32_t(const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
-                                 cudaStream_t st) {
+static cudaError_t launch_tf32_t(const void* tmap_mn, const GradParams& g, int ctas, cudaStream_t st) {
   using G = Tf32Geom<H>;
   static bool attr_done[64] = {};
   int dev = 0;
@@ -600,7 +593,7 @@ static cudaError_t launch_tf32_t(const void* tmap_mn, const GradParams& g, int c
     attr_done[dev] = true;
   }
   return launch_chain_kernel(grad_tf32_kernel<H, false>, dim3(ctas), dim3(TF32_THREADS), G::SMEM, st,
-                             *reinterpret_cast<const CUtensorMap*>(tmap_mn), g, dbg);
+                             *reinterpret_cast<const CUtensorMap*>(tmap_mn), g);
 }
 
 // Several leapfrog steps of one window in one COOPERATIVE launch (every CTA resident: the grid barrier
@@ -637,13 +630,11 @@ cudaError_t launch_grad_tf32_multistep(int H, const void* tmap_mn, const GradPar
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, grad_tf32_kernel<40, true>, *reinterpret_cast<const CUtensorMap*>(tmap_mn), g,
-                            (float*)nullptr);
+  return cudaLaunchKernelEx(&cfg, grad_tf32_kernel<40, true>, *reinterpret_cast<const CUtensorMap*>(tmap_mn), g);
 }
 
-cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, float* dbg,
-                             cudaStream_t st) {
-  if (H == 40) return launch_tf32_t<40>(tmap_mn, g, ctas, dbg, st);
+cudaError_t launch_grad_tf32(int H, const void* tmap_mn, const GradParams& g, int ctas, cudaStream_t st) {
+  if (H == 40) return launch_tf32_t<40>(tmap_mn, g, ctas, st);
   if (H == 128) return launch_grad_tf32_wide(tmap_mn, g, ctas, st);  // grad_tf32_wide.cu
   return cudaErrorInvalidValue;
 }
