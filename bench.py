@@ -37,6 +37,7 @@ LEAPFROG = 10
 EPS = 1e-3
 SEED = 2024
 ALG_BYTES_PER_ROW = 92          # 22 features + y, FP32: what one gradient must read per row
+MIN_TIMED_S = 2.0               # the K-step region is repeated until this much has been timed
 METRIC = "hmc_samples_per_sec_all_windows"
 UNIT = "samples/s"
 # DRAM traffic of the gradient kernel per row, from the ncu capture summarised in
@@ -112,14 +113,35 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def host_threads():
+    """Host cores this process may use.  Not OpenMP's default: launchers such as torch.distributed.run
+    export OMP_NUM_THREADS=1, which would put the CPU arm on one core."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
+
+def cpu_window(rows=None):
+    """One synthetic window for the CPU arm: same shapes and distributions as the library's generator
+    (X ~ N(0,1), y = teacher MLP(X) + N(0, 0.05^2), teacher ~ N(0, 0.3^2)), drawn with numpy so that this
+    arm loads nothing but the oracle."""
+    rows = ROWS if rows is None else rows
+    rng = np.random.default_rng(SEED)
+    x = rng.standard_normal((rows, D)).astype(np.float32)
+    t = (0.3 * rng.standard_normal(P)).astype(np.float32)
+    h = np.tanh(x @ t[:D * H].reshape(D, H) + t[D * H:D * H + H])
+    y = (h @ t[D * H + H:D * H + 2 * H] + t[-1] + 0.05 * rng.standard_normal(rows)).astype(np.float32)
+    return x, y
+
+
 def cpu_port_rate(seconds_budget, nthreads=0, max_iters=4096):
     """Samples/s of the FP32 CPU port (oracle/) on ONE window of the same workload."""
-    import mcmc_bnn_example_b200 as m
     import oracle as O
-    x, y, _ = m.synth_window(SEED, 0, ROWS)
+    x, y = cpu_window()
     model, sampler = O.baseline_model(), O.baseline_sampler(L=LEAPFROG, eps=EPS)
     rng = np.random.default_rng(0)
-    threads = O.max_threads() if nthreads <= 0 else nthreads
+    threads = host_threads() if nthreads <= 0 else nthreads
     # one warm-up iteration, then as many as fit the budget
     mom = rng.standard_normal((1, P)).astype(np.float32)
     lu = np.log(rng.uniform(size=1)).astype(np.float32)
@@ -382,29 +404,50 @@ def main():
                                     is_device=False, global_window=w0 + i)
 
     # ---------------- device-resident measurement ----------------
+    # A timed region is EXACTLY K steps between a barrier + synchronize on both sides.  K steps of this
+    # workload last only tens of milliseconds, too short for the clocks to settle under the power cap and
+    # for more than a couple of clock samples, so the region is repeated back to back until at least
+    # MIN_TIMED_S seconds have been timed: `ms_per_step` / `value` are the MEDIAN region (the sustained
+    # rate the 800-step workload sees), the fastest region is reported beside it as the burst figure.
     ctx = make_ctx(0)
     upload(ctx)
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
     ctx.run_chain(W)  # bootstrap + warm-up iterations (graph capture happens here)
     ctx.launch_count(reset=True)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     sampler = ClockSampler(local_rank)
-    barrier()
-    torch.cuda.synchronize()
+
+    def timed_region():
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        torch.cuda.synchronize()
+        e0.record(stream)
+        ctx.run_chain(K, sync=False)
+        e1.record(stream)
+        ctx.synchronize()
+        torch.cuda.synchronize()
+        barrier()
+        return e0.elapsed_time(e1)
+
     sampler.start()
-    e0.record(stream)
-    ctx.run_chain(K, sync=False)
-    e1.record(stream)
-    ctx.synchronize()
-    torch.cuda.synchronize()
-    barrier()
+    regions = [timed_region()]
+    launches = ctx.launch_count()          # of ONE region: the claim is per K steps
+    n_rep = int(min(400, max(1, np.ceil(MIN_TIMED_S * 1e3 / max(regions[0], 1e-3)))))
+    if dist is not None:                   # every rank repeats the same number of times
+        t = torch.tensor([n_rep], device=dev, dtype=torch.int64)
+        dist.broadcast(t, src=0)
+        n_rep = int(t[0])
+    for _ in range(n_rep - 1):
+        regions.append(timed_region())
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1)
-    launches = ctx.launch_count()
     geom = ctx.geometry()
     acc = [ctx.chain_info(i)["accepted"] for i in range(min(n_local, 4))]
     ctx.close()
     del ctx
+    if dist is not None:                   # a region's time is the slowest rank's
+        t = torch.tensor(regions, device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        regions = [float(v) for v in t]
+    ms = float(np.median(regions))
 
     # ---------------- end-to-end through the C-ABI with host buffers ----------------
     e2e_ms = None
@@ -432,9 +475,9 @@ def main():
 
     # ---------------- reduce over ranks: max time, summed bytes/launches ----------------
     if dist is not None:
-        t = torch.tensor([ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
+        t = torch.tensor([e2e_ms or 0.0], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms, e2e_max = float(t[0]), float(t[1])
+        e2e_max = float(t[0])
         s = torch.tensor([float(launches), float(h2d), float(d2h)], device=dev, dtype=torch.float64)
         dist.all_reduce(s, op=dist.ReduceOp.SUM)
         launches, h2d, d2h = int(s[0]), int(s[1]), int(s[2])
@@ -457,6 +500,11 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": K, "warmup": W,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": args.precision, "data": "synthetic",
+        "timing": {"regions": len(regions), "region_steps": K, "timed_s": sum(regions) * 1e-3,
+                   "ms_per_step_median": ms / K, "ms_per_step_min": min(regions) / K,
+                   "ms_per_step_max": max(regions) / K,
+                   "note": "value and ms_per_step are the median over back-to-back K-step regions (sustained "
+                           "under the power cap); ms_per_step_min is the burst figure"},
         "config": {
             "workload": ("BASELINE configs[2]: 200 windows x 58368 rows x 22 features FP32, 22-40-1 MLP "
                          "(961 params), Gaussian sigma=1, N(0,1) prior, L=10, eps=1e-3, windows sharded "
@@ -486,10 +534,11 @@ def main():
     if e2e_ms is not None:
         out["e2e"] = {"value": args.windows * K / (e2e_ms * 1e-3), "unit": UNIT,
                       "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,
-                      "note": "one run_chain call per measurement on a context created beforehand "
-                              "(allocation is not timed): dataset upload from pinned host memory once, "
-                              "K iterations, K samples per window read back; bytes are totals over "
-                              "GPUs divided by K"}
+                      "note": "one measurement = on a context created beforehand (allocation is not timed) the "
+                              "dataset upload from pinned host memory, bootstrap + K iterations and the "
+                              "read-back of K samples per window.  The upload happens ONCE per K steps: "
+                              "its cost is amortised over K, so this value rises with --steps (the real "
+                              "workload runs 800 steps per upload); bytes are totals over GPUs divided by K"}
     if not args.no_cpu:
         r, threads, n, dt = cpu_port_rate(12.0)
         out["cpu_baseline"] = {

@@ -13,6 +13,9 @@
 //     variant leaves them with (L-1 rotations, mcmc_step_ffma.h:382-393) in both
 //     precisions, so the TC-only replay of main.h:224-227 must not be done;
 //     grad_prev's contents after the call are unspecified;
+//   * mcmc_step recognises the dataset by the two pointers x.ptr() / y.ptr() and keeps a repacked
+//     copy: a caller that refills the SAME DeviceMatrix objects with another window must call
+//     mcmc::rebind_data() before the next mcmc_step (the reference re-reads x and y every launch);
 //   * main_loop reads DATA_FNAME in the reference's text layout when that file
 //     is present (mcmc_b200_read_table) and otherwise generates a synthetic
 //     window (the reference's data file is not distributed); either way the
@@ -36,9 +39,24 @@ inline void check(int status, const char* what) {
   if (status != MCMC_B200_OK) throw std::runtime_error(std::string(what) + ": " + mcmc_b200_last_error());
 }
 
+// The library's reference preset with every constant of global_params.h applied on top (they are
+// equal unless the header was configured on the command line).
 inline mcmc_b200_config reference_config() {
   mcmc_b200_config cfg;
   mcmc_b200_config_reference(&cfg);
+  cfg.D = FEAT_DIM[0];
+  cfg.H = FEAT_DIM[1];
+  cfg.lik_scale = STUDENT_T_SCALE;
+  cfg.lik_df = STUDENT_T_DF;
+  cfg.prior_scale = PRIOR_SCALE;
+  cfg.leapfrog_steps = LEAPFROG_STEPS;
+  cfg.burn_in = BURN_IN_STEPS;
+  cfg.adapt_steps = STEP_SIZE_ADAPT_STEPS;
+  cfg.sample_capacity = SAMPLE_STEPS;
+  cfg.eps0 = STEP_SIZE_INIT;
+  cfg.target_rate = STEP_SIZE_TARGET_RATE;
+  cfg.decrement = STEP_SIZE_DECREMENT;
+  cfg.increment = STEP_SIZE_INCREMENT;
 #ifdef USE_TC
   cfg.precision = MCMC_B200_PREC_TF32;
 #endif
@@ -112,6 +130,9 @@ void mcmc_step(const DeviceMatrix<T>& x, const DeviceMatrix<T>& y, DeviceMatrix<
                             (void*)stream),
         "mcmc_step");
 }
+
+// The next mcmc_step repacks x / y even when they are the same buffers as before (see the list above).
+inline void rebind_data() { check(mcmc_b200_rebind_data(step_context()), "rebind_data"); }
 
 }  // namespace mcmc
 

@@ -250,6 +250,16 @@ int mcmc_b200_mcmc_step(mcmc_b200_ctx* ctx, const float* x, const float* y, cons
                         const float* grad_prev, float* grad_cur, float* grad_next,
                         float* loss_values, int L, float eps, void* stream);
 /*
+ * mcmc_b200_mcmc_step keeps a repacked copy of the dataset and recognises the
+ * dataset by its two POINTERS: it repacks on the first call and whenever x or
+ * y is a different address, not when the contents behind the same addresses
+ * change.  A caller that loads the next window into the same buffers (the
+ * "sequential passes" of main.h:302-307) calls this first: the next mcmc_step
+ * repacks.  The reference reads x and y afresh on every launch and needs no
+ * such call (mcmc_step_ffma.h:76-104).
+ */
+int mcmc_b200_rebind_data(mcmc_b200_ctx* ctx);
+/*
  * Drop-in for mcmc::log_acpt_prec (kernel_helpers.h:153-188) on DEVICE
  * buffers: sum(new_loss - prev_loss) over n_loss entries plus the kinetic
  * difference with the closing half kick; returns the scalar on the host
@@ -296,12 +306,36 @@ float mcmc_b200_philox_normal(uint64_t seed, uint32_t window, uint32_t iteration
                               uint32_t index);
 void mcmc_b200_philox_raw(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
 
+/*
+ * The same generator evaluated ON THE DEVICE, for tests that compare the two:
+ * n (1..4096, n*5+1 <= the context's padded row count) raw Philox blocks for
+ * counters {ctr[0]+i, ctr[1], ctr[2], ctr[3]}, the n momentum normals the accept
+ * kernel draws for (seed = key, window = ctr[2], iteration = ctr[1]) and that
+ * iteration's accept uniform.  Replaces nothing in the reference, whose
+ * streams are Thrust's and libstdc++'s minstd engines (main.h:207-216,235-239).
+ */
+int mcmc_b200_philox_device(mcmc_b200_ctx* ctx, const uint32_t ctr[4], const uint32_t key[2], int n,
+                            uint32_t* raw_out, float* normals_out, float* uniform_out);
+
 /* Counters for benchmarks: kernels of this library launched on the context
  * since creation (or since the last reset of the counter). */
 int64_t mcmc_b200_launch_count(mcmc_b200_ctx* ctx, int reset);
-/* Average device time in ms of the dominant (gradient) kernel over the last
- * run_chain call, from CUDA events on the launching stream; <0 if unknown. */
+/* How the context's chain launches are cut: partial-gradient slots per window,
+ * resident CTAs per SM of the gradient kernel, rows per tile.  Any may be null. */
 int mcmc_b200_chain_geometry(mcmc_b200_ctx* ctx, int* slices, int* ctas_per_sm, int* tile_rows);
+
+/*
+ * Self-test of the device-side time-out route.  Every wait inside the kernels
+ * is bounded (the reference's grid barrier spins without a limit,
+ * mcmc_step_tc.h:597-612): a wait that runs out records a code in the
+ * context's status word, the kernel finishes by itself, and the next
+ * synchronising call returns MCMC_B200_ERR_TIMEOUT.  This call launches one
+ * small kernel that waits, with the kernels' own wait routine and a limit of
+ * limit_us microseconds (20 .. 1000000), on a barrier that nothing arms, and
+ * returns what the context then reports: MCMC_B200_ERR_TIMEOUT when the route
+ * works.  The status word is cleared on the way out: the context stays usable.
+ */
+int mcmc_b200_selftest_wait_timeout(mcmc_b200_ctx* ctx, int limit_us);
 
 #ifdef __cplusplus
 }

@@ -39,7 +39,8 @@ EXPORTS = [
     "mcmc_b200_log_acpt", "mcmc_b200_synth_window", "mcmc_b200_philox_normal", "mcmc_b200_philox_raw",
     "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
     "mcmc_b200_checkpoint_size", "mcmc_b200_checkpoint_save", "mcmc_b200_checkpoint_load",
-    "mcmc_b200_read_table", "mcmc_b200_plan_work_table",
+    "mcmc_b200_read_table", "mcmc_b200_plan_work_table", "mcmc_b200_rebind_data",
+    "mcmc_b200_selftest_wait_timeout", "mcmc_b200_philox_device",
 ]
 
 
@@ -362,6 +363,27 @@ class Context:
                                          _vp(mom_prev), _vp(mom_next), _vp(grad_prev), _vp(grad_cur),
                                          _vp(grad_next), _vp(loss_values), L, C.c_float(eps),
                                          _vp(stream if stream is not None else self.stream)))
+
+    def rebind_data(self):
+        """The next mcmc_step repacks the dataset even when x and y are the same pointers as before."""
+        _check(lib().mcmc_b200_rebind_data(self._h))
+
+    def selftest_wait_timeout(self, limit_us=1000):
+        """Runs a bounded device-side wait into its limit; returns the status code the context reports
+        (4 = MCMC_B200_ERR_TIMEOUT when the time-out route works) and its message."""
+        code = lib().mcmc_b200_selftest_wait_timeout(self._h, int(limit_us))
+        return code, lib().mcmc_b200_last_error().decode()
+
+    def philox_device(self, ctr, key, n):
+        """The device's evaluation of the random streams: (raw [n][4] uint32, normals [n], accept uniform)."""
+        c = (C.c_uint32 * 4)(*ctr)
+        k = (C.c_uint32 * 2)(*key)
+        raw = np.empty((n, 4), np.uint32)
+        nrm = np.empty(n, np.float32)
+        u = C.c_float()
+        _check(lib().mcmc_b200_philox_device(self._h, c, k, n, raw.ctypes.data_as(C.POINTER(C.c_uint32)),
+                                             _fp(nrm), C.byref(u)))
+        return raw, nrm, u.value
 
     def log_acpt(self, prev_loss, new_loss, n_loss, prev_mom, new_mom, grad_cur, eps, stream=None):
         """mcmc::log_acpt_prec on device pointers (ints); returns the host scalar."""

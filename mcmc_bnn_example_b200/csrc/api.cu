@@ -258,6 +258,12 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
   if (cfg->leapfrog_steps < 1 || cfg->lik_scale <= 0 || cfg->prior_scale <= 0)
     return fail(MCMC_B200_ERR_INVALID, "bad sampler/model constants");
   if (n_windows > 65535) return fail(MCMC_B200_ERR_INVALID, "at most 65535 windows per context");
+  {
+    // the kernels index rows of the whole context with 32-bit integers (TMA coordinates, tile numbers)
+    const long long rp = (rows + TF32_TILE - 1) / TF32_TILE * TF32_TILE;
+    if (rows > 0x7fffffffLL - TF32_TILE || rp * (long long)n_windows > 0x7fffffffLL)
+      return fail(MCMC_B200_ERR_INVALID, "rows per window x windows must stay below 2^31 rows per context");
+  }
   int ndev = 0;
   cudaError_t e0 = cudaGetDeviceCount(&ndev);
   if (e0 != cudaSuccess || ndev == 0)
@@ -536,6 +542,35 @@ API int mcmc_b200_synchronize(mcmc_b200_ctx* c) {
   return check_status(c);
 }
 
+API int mcmc_b200_philox_device(mcmc_b200_ctx* c, const uint32_t ctr[4], const uint32_t key[2], int n,
+                                uint32_t* raw_out, float* normals_out, float* uniform_out) {
+  if (!c || !ctr || !key || n < 1 || n > 4096 || !raw_out || !normals_out || !uniform_out)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  // scratch of this call: the single-window row-loss buffer is at least 128 floats and is free between calls
+  if ((size_t)n * 5 + 1 > (size_t)c->rows_pad) return fail(MCMC_B200_ERR_INVALID, "n too large for this context");
+  uint32_t* raw = reinterpret_cast<uint32_t*>(c->row_loss);
+  float* normals = c->row_loss + 4 * (size_t)n;
+  float* uni = normals + n;
+  cudaError_t e = launch_philox_probe(ctr, key, n, raw, normals, uni, c->stream);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  CK(cudaMemcpyAsync(raw_out, raw, (size_t)n * 16, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaMemcpyAsync(normals_out, normals, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaMemcpyAsync(uniform_out, uni, 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_selftest_wait_timeout(mcmc_b200_ctx* c, int limit_us) {
+  if (!c || limit_us < 20 || limit_us > 1000000) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  CK(cudaSetDevice(c->device));
+  cudaError_t e = launch_wait_probe(c->status, (unsigned int)(limit_us / 20), c->stream);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  return check_status(c);
+}
+
 API int mcmc_b200_set_window_data(mcmc_b200_ctx* c, int window, int64_t global_window, const float* x,
                                   const float* y, int is_device) {
   if (!c || !x || !y || window < 0 || window >= c->W) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
@@ -754,10 +789,19 @@ static int bootstrap(mcmc_b200_ctx* c) {
   return MCMC_B200_OK;
 }
 
+// The captured iteration graph bakes in the launch sequence (with or without the partial-sum and
+// all-reduce launches, one launch per step or one per iteration): whatever changes that sequence drops it.
+static void drop_graph(mcmc_b200_ctx* c) {
+  if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
+  c->graph_exec = nullptr;
+  c->graph_tried = false;
+}
+
 API int mcmc_b200_reset_chain(mcmc_b200_ctx* c) {
   if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
   CK(cudaSetDevice(c->device));
   CK(cudaStreamSynchronize(c->stream));
+  drop_graph(c);
   c->bootstrapped = false;
   c->iters_done = 0;
   return MCMC_B200_OK;
@@ -983,11 +1027,12 @@ API int mcmc_b200_checkpoint_load(mcmc_b200_ctx* c, const void* host_buf, uint64
 static int explicit_steps(mcmc_b200_ctx* c, int data_window, int L, float eps, const float* w0,
                           const float* m0, const float* g0, float* w_last, float* m_last,
                           float* g_out, float* row_loss, float* prior_loss, cudaStream_t st,
-                          bool eval_only) {
+                          bool eval_only, bool data_fresh = false) {
   const int S = c->slices_x;
   for (int s = 0; s < L; ++s) {
     GradParams g = base_grad_params(c);
     g.data_window0 = data_window;
+    g.data_fresh = (data_fresh && s == 0) ? 1 : 0;  // a repack was queued directly before the first launch
     g.mode = eval_only ? MODE_EVAL : (s == 0 ? MODE_FIRST : MODE_NEXT);
     g.w_in = s == 0 ? w0 : c->xw[s & 1];
     g.m_in = s == 0 ? m0 : c->xm[s & 1];
@@ -1091,19 +1136,29 @@ API int mcmc_b200_mcmc_step(mcmc_b200_ctx* c, const float* x, const float* y, co
   if (c->W != 1) return fail(MCMC_B200_ERR_INVALID, "mcmc_step needs a context with one window");
   CK(cudaSetDevice(c->device));
   cudaStream_t st = (cudaStream_t)stream;
+  bool repacked = false;
   if (x != c->bound_x || y != c->bound_y) {
-    // first use of this dataset: repack it (io.h:82-85 is where the reference uploads it)
+    // first use of this dataset (or the first call after mcmc_b200_rebind_data): repack it
+    // (io.h:82-85 is where the reference uploads it)
     cudaError_t e = launch_repack(x, y, c->xaug, c->rows, c->rows_pad, c->cfg.D, st);
     c->launches++;
     if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
     c->bound_x = x;
     c->bound_y = y;
     c->window_set[0] = 1;
+    repacked = true;
   }
   int r = explicit_steps(c, 0, L, eps, weights_prev, mom_prev, grad_prev, weights_next, mom_next, grad_cur,
-                         loss_values, loss_values ? loss_values + c->rows : nullptr, st, false);
+                         loss_values, loss_values ? loss_values + c->rows : nullptr, st, false, repacked);
   if (r) return r;
   if (grad_next) CK(cudaMemsetAsync(grad_next, 0, (size_t)c->P * 4, st));
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_rebind_data(mcmc_b200_ctx* c) {
+  if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
+  c->bound_x = nullptr;
+  c->bound_y = nullptr;
   return MCMC_B200_OK;
 }
 
@@ -1196,6 +1251,7 @@ API int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* c, const unsigned char id[1
   c->rank = rank;
   c->nranks = nranks;
   c->multistep = false;  // every step's sums cross GPUs: one launch + one all-reduce per step
+  drop_graph(c);         // a graph captured before this call has neither the sums nor the all-reduce in it
   return MCMC_B200_OK;
 }
 

@@ -77,8 +77,10 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
     n = 0;
     for (int p = tid; p < a.P; p += ACC_THREADS, ++n) a.g_out[p] = gv[n];
     if (tid == 0) {
-      a.scalars_out[0] = ll_new;
-      a.scalars_out[1] = lp_new;
+      // a bounded wait that ran out left the sums incomplete: say so in the result itself
+      const bool bad = a.status_in && *a.status_in != 0;
+      a.scalars_out[0] = bad ? (double)NAN : ll_new;
+      a.scalars_out[1] = bad ? (double)NAN : lp_new;
     }
     return;
   }
@@ -141,6 +143,46 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
 
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st) {
   return launch_chain_kernel(hmc_accept_kernel, dim3(windows), dim3(ACC_THREADS), 0, st, a);
+}
+
+// ---- bounded-wait self-test ------------------------------------------------
+// One CTA waits, with the gradient kernels' own mbar_wait, on a barrier that nothing ever arms: the wait
+// runs out after `slices` slices of 20 us, records its code in the status word and the kernel returns by
+// itself.  This is how the time-out route (status word -> MCMC_B200_ERR_TIMEOUT -> context still usable)
+// is exercised without any fault, trap or unbounded wait (the reference's barrier spins without a limit,
+// mcmc_step_tc.h:597-612).
+__global__ void wait_probe_kernel(int* status, unsigned int slices) {
+  __shared__ __align__(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) mbar_wait(&bar, 0, status, 901, slices);
+}
+cudaError_t launch_wait_probe(int* status, unsigned int slices, cudaStream_t st) {
+  wait_probe_kernel<<<1, 32, 0, st>>>(status, slices);
+  return cudaGetLastError();
+}
+
+// ---- the device's random streams, for comparison with the host's ------------------------
+// n raw Philox blocks for counters {ctr0 + i, ctr1, ctr2, ctr3}, and the n momentum normals / the accept
+// uniform the accept kernel would draw for (seed, window, iteration): same functions, run on the device.
+__global__ void philox_probe_kernel(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1,
+                                    int n, uint32_t* raw, float* normals, float* uniform) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const Philox4 r = philox4x32_10(c0 + (uint32_t)i, c1, c2, c3, k0, k1);
+  for (int q = 0; q < 4; ++q) raw[4 * i + q] = r.v[q];
+  const uint64_t seed = ((uint64_t)k1 << 32) | k0;
+  normals[i] = philox_normal(seed, c2, c1, STREAM_MOMENTUM, (uint32_t)i);
+  if (i == 0) *uniform = philox_accept_uniform(seed, c2, c1);
+}
+cudaError_t launch_philox_probe(const uint32_t ctr[4], const uint32_t key[2], int n, uint32_t* raw, float* normals,
+                                float* uniform, cudaStream_t st) {
+  philox_probe_kernel<<<(n + 127) / 128, 128, 0, st>>>(ctr[0], ctr[1], ctr[2], ctr[3], key[0], key[1], n, raw,
+                                                       normals, uniform);
+  return cudaGetLastError();
 }
 
 // ---- dataset repack ------------------------------------------------------

@@ -50,6 +50,7 @@ struct AcceptParams {
   float* g_out;              // [P]
   float* prior_loss_out;     // optional [P]
   double* scalars_out;       // [2]: loglik, logprior
+  const int* status_in;      // optional: device error word; when it is set the scalars come out as NaN
 };
 
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st);
@@ -60,6 +61,9 @@ cudaError_t launch_reduce_partials(const float* partial, const double* ll_partia
                                    cudaStream_t st);
 cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
                            float* out, cudaStream_t st);
+cudaError_t launch_philox_probe(const uint32_t ctr[4], const uint32_t key[2], int n, uint32_t* raw, float* normals,
+                                float* uniform, cudaStream_t st);
+cudaError_t launch_wait_probe(int* status, unsigned int slices, cudaStream_t st);
 cudaError_t launch_log_acpt(const float* prev_loss, const float* new_loss, long long n_loss,
                             const float* prev_mom, const float* new_mom, const float* grad_cur, int P,
                             float eps, float* out, cudaStream_t st);

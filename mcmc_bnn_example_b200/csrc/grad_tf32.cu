@@ -65,9 +65,9 @@ namespace mcmc_b200 {
 constexpr int TF32_NWG = 3;                            // compute warpgroups
 constexpr int TF32_THREADS = TF32_NWG * 128 + 128;      // + a control warpgroup (one warp per compute warpgroup, one idle)
 // registers: 512 threads start with 128 each; the control warpgroup hands most of its share to the
-// compute warpgroups (3 * 128 * 152 + 128 * 56 = 65536)
-constexpr int TF32_COMPUTE_REGS = 152;
-constexpr int TF32_CTRL_REGS = 56;
+// compute warpgroups (3 * 128 * 160 + 128 * 32 = 65536)
+constexpr int TF32_COMPUTE_REGS = 160;
+constexpr int TF32_CTRL_REGS = 32;
 constexpr int TF32_NST = 3;                            // TMA stages per warpgroup
 
 template <int H>
@@ -357,12 +357,13 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       fence_proxy_async_smem();
       __syncthreads();  // S1
 
-      // output-layer weights live in registers for the whole segment
-      float w1r[H];
+      // output-layer weights live in registers for the whole segment, two per register pair
+      uint64_t w1p[H / 2];
 #pragma unroll
       for (int j = 0; j < H; j += 4) {
         const float4 v = *reinterpret_cast<const float4*>(w1s + j);
-        w1r[j] = v.x; w1r[j + 1] = v.y; w1r[j + 2] = v.z; w1r[j + 3] = v.w;
+        w1p[j >> 1] = pack2(v.x, v.y);
+        w1p[(j >> 1) + 1] = pack2(v.z, v.w);
       }
       const float b1 = b1s;
       uint64_t dw1p[H / 2];  // dW1 accumulators, two hidden units per register pair
@@ -410,24 +411,27 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         const int t = t0 + wg + i * NWG;
         ok = ok && mbar_wait_q(&bar_fwd[wg], n & 1, g.status, 202);
         tc_fence_after();
-        // forward(n) is done with the A operand: the next tile's rows go in now, and once Z(n) is in
-        // registers forward(n+1) may overwrite the accumulator: it has this whole tile's epilogue to complete
-        float y_next = 0.f;
-        if (i + 1 < my_nt) y_next = stage_row();
+        // Z(n) starts moving into registers; while it does, forward(n) being done with the A operand, the
+        // next tile's rows go into tensor memory.  The control warp is told only after the tanh pass (the
+        // tensor-memory stores have landed by then): forward(n+1) overwrites the accumulator, which is safe once
+        // Z(n) is in registers, and still has the rest of this tile's epilogue to complete.
         float z[H];
 #pragma unroll
         for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
+        float y_next = 0.f;
+        if (i + 1 < my_nt) y_next = stage_row();
         tc_wait_ld();
-        if (i + 1 < my_nt) publish_row();
-        float pred = b1, pred1 = 0.f;
+        uint64_t pred2 = pack2(b1, 0.f);
 #pragma unroll
         for (int j = 0; j < H; j += 2) {
           z[j] = tanh_fast(z[j]);
           z[j + 1] = tanh_fast(z[j + 1]);
-          pred = fmaf(w1r[j], z[j], pred);
-          pred1 = fmaf(w1r[j + 1], z[j + 1], pred1);
+          pred2 = fma2(w1p[j >> 1], pack2(z[j], z[j + 1]), pred2);
         }
+        float pred, pred1;
+        unpack2(pred2, pred, pred1);
         pred += pred1;
+        if (i + 1 < my_nt) publish_row();
         const int grow = t * TF32_TILE + wtid;
         const bool valid = grow < g.n_rows;
         float loss, dy;

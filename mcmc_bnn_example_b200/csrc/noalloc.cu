@@ -20,6 +20,11 @@
 // (everything a call reads it first overwrites, and the status word is cleared
 // on every call), and two calls that overlap on the same GPU — different
 // streams, or different host threads — race on it.  Serialise them.
+//
+// Errors after the call has returned: the call only queues work.  If a bounded
+// device-side wait runs out, the kernel records it in the scratch's status word
+// and the last kernel of the call writes NaN into both output scalars, so a
+// caller that cannot query anything else still sees that the result is void.
 #include <cuda_runtime.h>
 #include <math.h>
 #include <string.h>
@@ -129,6 +134,7 @@ extern "C" __attribute__((visibility("default"))) int mcmc_b200_potential_and_gr
   g.partial_out = partial;
   g.ll_out = llp;
   g.status = status;
+  g.data_fresh = 1;  // the repack above wrote xaug: the kernel fetches no row ahead of its dependency wait
   g.lik.kind = cfg->likelihood;
   g.lik.inv_scale = (float)(1.0 / cfg->lik_scale);
   if (cfg->likelihood == MCMC_B200_LIK_STUDENT_T) {
@@ -161,6 +167,7 @@ extern "C" __attribute__((visibility("default"))) int mcmc_b200_potential_and_gr
   a.prior = g.prior;
   a.g_out = grad;
   a.scalars_out = loglik_logprior;
+  a.status_in = status;  // a wait that ran out turns both scalars into NaN: the caller sees it in the result
   e = launch_accept(a, 1, st);
   if (e != cudaSuccess) return fail_static(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
   return MCMC_B200_OK;

@@ -138,33 +138,44 @@ def test_leapfrog_matches_oracle_mcmc_step(built, prec, L):
     ctx.close()
 
 
+@pytest.mark.parametrize("prec", [0, 1])
 @pytest.mark.parametrize("preset", ["baseline", "reference"])
-def test_accept_decisions_identical_over_first_50_iterations(built, preset):
-    """The device chain replayed on the CPU with the draws the device used."""
+def test_accept_decisions_identical_over_first_50_iterations(built, preset, prec):
+    """The device chain replayed on the CPU with the draws the device used, in both precisions (the oracle
+    runs in the same mode: TF32 truncates the tensor-core operands as the device does)."""
     m, O = built
     rows, n_iter = 58368 if preset == "baseline" else 8192, 50
     x, y, _ = m.synth_window(9, 0, rows)
+    tf = bool(prec)
     if preset == "baseline":
-        cfg = m.baseline_config(sample_capacity=n_iter, trace_iters=n_iter, seed=1234)
-        model, sampler = O.baseline_model(), O.baseline_sampler()
+        cfg = m.baseline_config(precision=prec, sample_capacity=n_iter, trace_iters=n_iter, seed=1234)
+        model, sampler = O.baseline_model(tf32=tf), O.baseline_sampler()
     else:
         # the reference's Student-t / N(0,200^2) preset with its adaptive burn-in, shortened to
         # L = 10 so that the CPU replay finishes in seconds; eps0 = 0.2 gives accepts, rejections and both
         # branches of the step-size adaptation within 50 iterations
-        cfg = m.reference_config(leapfrog_steps=10, burn_in=0, adapt_steps=30, sample_capacity=n_iter,
-                                 trace_iters=n_iter, seed=99, eps0=0.2)
+        cfg = m.reference_config(precision=prec, leapfrog_steps=10, burn_in=0, adapt_steps=30,
+                                 sample_capacity=n_iter, trace_iters=n_iter, seed=99, eps0=0.2)
         x = x * np.float32(0.05)
-        model, sampler = O.reference_model(), O.Sampler(10, 30, 0.2, 0.2, 0.1, 0.01)
+        model, sampler = O.reference_model(tf32=tf), O.Sampler(10, 30, 0.2, 0.2, 0.1, 0.01)
     ctx = m.Context(cfg, n_windows=1, rows=rows)
     ctx.set_window_data(0, x, y)
     ctx.run_chain(n_iter)
     tr = ctx.get_trace(0)
     samples = ctx.get_samples(0, 0, n_iter)
     ref = O.hmc_chain(model, sampler, x, y, tr["momenta"], tr["log_u"])
-    assert np.array_equal(tr["accepted"], ref["accepted"])
+    differ = np.flatnonzero(tr["accepted"] != ref["accepted"])
+    margin = np.abs(ref["log_acpt"] - tr["log_u"])
+    assert differ.size == 0, ("decisions differ at iterations %s; |log_acpt - log_u| there: %s; device "
+                              "log_acpt %s, oracle %s" % (differ, margin[differ], tr["log_acpt"][differ],
+                                                           ref["log_acpt"][differ]))
     assert np.allclose(tr["eps"], ref["eps"], rtol=1e-6)
-    assert np.allclose(tr["log_acpt"], ref["log_acpt"], rtol=1e-3, atol=2e-2)
-    assert np.allclose(samples, ref["samples"], rtol=1e-4, atol=1e-5)
+    if prec == 0:
+        assert np.allclose(tr["log_acpt"], ref["log_acpt"], rtol=1e-3, atol=2e-2)
+        assert np.allclose(samples, ref["samples"], rtol=1e-4, atol=1e-5)
+    else:
+        # same decisions, so the two chains visit the same states up to the TF32 mode's per-call tolerance
+        assert np.abs(samples - ref["samples"]).max() <= TOL[1] * max(1e-3, np.abs(ref["samples"]).max())
     info = ctx.chain_info(0)
     assert info["iterations"] == n_iter and info["accepted"] == int(ref["accepted"].sum())
     if preset == "reference":
@@ -174,37 +185,92 @@ def test_accept_decisions_identical_over_first_50_iterations(built, preset):
     ctx.close()
 
 
+def _host_accept_log_u(m, seed, gwin, it):
+    """log of the accept uniform of (seed, window, iteration), from the host's Philox."""
+    r = m.philox_raw([0, it, gwin, 1], [seed & 0xFFFFFFFF, seed >> 32])
+    u = np.float32((np.float32(r[0] >> 8) + np.float32(1.0)) * np.float32(1.0 / 16777216.0))
+    return np.log(u, dtype=np.float32)
+
+
+def test_device_random_streams_equal_the_host_functions(built):
+    """Momentum normals and accept uniforms drawn inside the accept kernel are the host functions'
+    values for (seed, GLOBAL window, iteration): raw Philox words bit-exact, normals to 2e-6 relative (the device
+    uses sincospif, the host sinf/cosf), log-uniforms to float rounding."""
+    m, _ = built
+    rows, n_iter, W, seed = 512, 6, 3, 0x1234567ABCDEF
+    gwins = (7, 1000, 65536 + 3)
+    cfg = m.baseline_config(sample_capacity=n_iter, trace_iters=n_iter, seed=seed)
+    ctx = m.Context(cfg, n_windows=W, rows=rows)
+    for w in range(W):
+        x, y, _ = m.synth_window(3, w, rows)
+        ctx.set_window_data(w, x, y, global_window=gwins[w])
+    ctx.run_chain(n_iter)
+    key = [seed & 0xFFFFFFFF, seed >> 32]
+    for w in range(W):
+        tr = ctx.get_trace(w)
+        for it in range(n_iter):
+            host = np.array([m.lib().mcmc_b200_philox_normal(seed, gwins[w], it, 0, p) for p in range(P)],
+                            np.float32)
+            assert np.all(np.abs(tr["momenta"][it] - host) <= 2e-6 * np.maximum(1.0, np.abs(host))), (w, it)
+            lu = _host_accept_log_u(m, seed, gwins[w], it)
+            assert abs(tr["log_u"][it] - lu) <= 1e-6 * max(1.0, abs(lu)), (w, it)
+        # the generator itself, evaluated on the device: bit-exact words
+        raw, nrm, u = ctx.philox_device([5, 2, gwins[w], 0], key, 100)
+        for i in (0, 1, 57, 99):
+            assert list(raw[i]) == m.philox_raw([5 + i, 2, gwins[w], 0], key)
+        host = np.array([m.lib().mcmc_b200_philox_normal(seed, gwins[w], 2, 0, p) for p in range(100)], np.float32)
+        assert np.all(np.abs(nrm - host) <= 2e-6 * np.maximum(1.0, np.abs(host)))
+        assert abs(np.log(np.float32(u)) - _host_accept_log_u(m, seed, gwins[w], 2)) <= 1e-6
+    ctx.close()
+
+
 @pytest.mark.parametrize("prec", [0, 1])
 def test_posterior_mean_prediction_over_800_samples(built, prec):
+    """Posterior-mean prediction over 800 samples against the CPU replay, three seeds.  The stated bound is
+    1 %.  It holds whenever the device chain and the replay take the same 800 decisions.  When they do
+    not (possible in TF32 mode only: a proposal whose ratio is within rounding of the draw), the two
+    chains decorrelate from that iteration on and the difference is Monte-Carlo, not kernel, error; its
+    size is measured in the same test as the oracle's own exact-vs-TF32 divergence on the same draws,
+    and the device must stay within 1.5x of it."""
     m, O = built
     rows, n_iter = 2048, 800
-    x, y, _ = m.synth_window(31, 0, rows)
-    cfg = m.baseline_config(precision=prec, sample_capacity=n_iter, trace_iters=n_iter, seed=5)
-    ctx = m.Context(cfg, n_windows=1, rows=rows)
-    ctx.set_window_data(0, x, y)
-    ctx.run_chain(n_iter)
-    tr = ctx.get_trace(0)
-    ref = O.hmc_chain(O.baseline_model(tf32=bool(prec)), O.baseline_sampler(), x, y, tr["momenta"],
-                      tr["log_u"])
-    assert ref["accepted"].sum() > n_iter // 2  # the chain moves
-    xs, _, _ = m.synth_window(31, 1, 512)
-    got = ctx.predict_mean(0, xs)
-    exp = O.predict_mean(O.baseline_model(), xs, ref["samples"])
-    rel_l2 = np.linalg.norm(got - exp) / np.linalg.norm(exp)
-    # FP32: the stated 1 %.  TF32: the device chain and the CPU replay take a different accept
-    # decision somewhere in 800 iterations and decorrelate from there; the oracle's own exact and
-    # TF32 modes differ by 1.1 - 1.5 % on this case for the same reason, so the bound for the
-    # tensor-core mode is the chain-divergence level, not a kernel error.
-    assert rel_l2 < (1e-2 if prec == 0 else 2.5e-2)
-    agree = np.mean(tr["accepted"] == ref["accepted"])
-    assert agree == 1.0 if prec == 0 else agree > 0.97
-    # and the device's own forward pass over its own samples is exact to FP32
-    own = O.predict_mean(O.baseline_model(), xs, ctx.get_samples(0))
-    assert np.linalg.norm(got - own) / np.linalg.norm(own) < 1e-5
-    ll, lp = ctx.final_loss(0, 0, 16)
-    ell, elp = O.final_loss(O.baseline_model(tf32=bool(prec)), x, y, ctx.get_samples(0, 0, 16))
-    assert abs(ll - ell) <= TOL[prec] * abs(ell) and abs(lp - elp) <= 1e-5 * abs(elp)
-    ctx.close()
+    for seed in (5, 6, 7):
+        x, y, _ = m.synth_window(31, 0, rows)
+        cfg = m.baseline_config(precision=prec, sample_capacity=n_iter, trace_iters=n_iter, seed=seed)
+        ctx = m.Context(cfg, n_windows=1, rows=rows)
+        ctx.set_window_data(0, x, y)
+        ctx.run_chain(n_iter)
+        tr = ctx.get_trace(0)
+        ref = O.hmc_chain(O.baseline_model(tf32=bool(prec)), O.baseline_sampler(), x, y, tr["momenta"],
+                          tr["log_u"])
+        assert ref["accepted"].sum() > n_iter // 2  # the chain moves
+        xs, _, _ = m.synth_window(31, 1, 512)
+        got = ctx.predict_mean(0, xs)
+        exp = O.predict_mean(O.baseline_model(), xs, ref["samples"])
+        rel_l2 = np.linalg.norm(got - exp) / np.linalg.norm(exp)
+        same = np.array_equal(tr["accepted"], ref["accepted"])
+        if prec == 0:
+            assert same and rel_l2 < 1e-2, (seed, rel_l2)
+        elif same:
+            assert rel_l2 < 1e-2, (seed, rel_l2)
+        else:
+            other = O.hmc_chain(O.baseline_model(tf32=False), O.baseline_sampler(), x, y, tr["momenta"],
+                                tr["log_u"])
+            exp2 = O.predict_mean(O.baseline_model(), xs, other["samples"])
+            own_div = np.linalg.norm(exp2 - exp) / np.linalg.norm(exp)
+            first = int(np.flatnonzero(tr["accepted"] != ref["accepted"])[0])
+            margin = abs(ref["log_acpt"][first] - tr["log_u"][first])
+            assert margin < 0.05, (seed, first, margin)  # only a borderline proposal may flip
+            assert rel_l2 <= max(1e-2, 1.5 * own_div), (seed, rel_l2, own_div)
+            assert np.mean(tr["accepted"] == ref["accepted"]) > 0.97
+        # and the device's own forward pass over its own samples is exact to FP32
+        own = O.predict_mean(O.baseline_model(), xs, ctx.get_samples(0))
+        assert np.linalg.norm(got - own) / np.linalg.norm(own) < 1e-5
+        if seed == 5:
+            ll, lp = ctx.final_loss(0, 0, 16)
+            ell, elp = O.final_loss(O.baseline_model(tf32=bool(prec)), x, y, ctx.get_samples(0, 0, 16))
+            assert abs(ll - ell) <= TOL[prec] * abs(ell) and abs(lp - elp) <= 1e-5 * abs(elp)
+        ctx.close()
 
 
 @pytest.mark.parametrize("prec", [0, 1])
@@ -452,3 +518,82 @@ def test_ragged_sizes_sweep(built, prec):
                 assert abs(got[i]["loglik"] - ref["loglik"]) <= tol * abs(ref["loglik"]) + 1e-6, (W, rows)
         # the partition changes the summation order only
         assert np.abs(outs[0][1] - outs[1][1]).max() <= 1e-4 * max(1e-3, np.abs(outs[1][1]).max()), (W, rows)
+
+
+def test_bounded_wait_runs_out_into_a_status_code_and_the_context_stays_usable(built):
+    """A device-side wait that nothing ever satisfies returns by itself after its limit, the context
+    reports MCMC_B200_ERR_TIMEOUT once, and the same context then evaluates a gradient correctly."""
+    m, O = built
+    rows = 3000
+    x, y, _ = m.synth_window(4, 0, rows)
+    w = _w(9)
+    for prec in (0, 1):
+        ctx = m.Context(m.baseline_config(precision=prec), n_windows=1, rows=rows)
+        ctx.set_window_data(0, x, y)
+        before = ctx.potential_and_grad(0, w)
+        code, msg = ctx.selftest_wait_timeout(limit_us=1000)
+        assert code == 4 and "901" in msg, (code, msg)
+        ctx.synchronize()  # the status word was cleared: no second report
+        after = ctx.potential_and_grad(0, w)
+        assert np.array_equal(before["grad"], after["grad"]) and before["loglik"] == after["loglik"]
+        ref = O.logp_grad(O.baseline_model(tf32=bool(prec)), x, y, w)
+        assert _grad_err(after["grad"], ref["grad"]) < TOL[prec]
+        ctx.run_chain(2)
+        assert ctx.chain_info(0)["iterations"] == 2
+        ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_mcmc_step_sees_a_dataset_overwritten_in_place_after_rebind(built, prec):
+    """mcmc_step recognises its dataset by the two pointers.  Refilling the same buffers with another
+    window must be announced with rebind_data(); without it the old repacked copy is used (documented)."""
+    import torch
+    m, O = built
+    rows, eps = 2048, 1e-3
+    cfg, model = _presets(m, O, prec)["baseline"]
+    dev = torch.device("cuda:0")
+    xa, ya, _ = m.synth_window(2, 0, rows)
+    xb, yb, _ = m.synth_window(2, 1, rows)
+    tx, ty = torch.from_numpy(xa).to(dev), torch.from_numpy(ya).to(dev)
+    w0 = _w(3)
+    zero = np.zeros(P, np.float32)
+    t = {k: torch.from_numpy(v).to(dev) for k, v in dict(wp=w0, mp=zero, gp=zero).items()}
+    out = {k: torch.zeros(P, device=dev) for k in ("wn", "mn", "gc", "gn")}
+    loss = torch.zeros(rows + P, device=dev)
+    ctx = m.Context(cfg, n_windows=1, rows=rows)
+    s = torch.cuda.current_stream().cuda_stream
+
+    def step():
+        ctx.mcmc_step(tx.data_ptr(), ty.data_ptr(), t["wp"].data_ptr(), out["wn"].data_ptr(),
+                      t["mp"].data_ptr(), out["mn"].data_ptr(), t["gp"].data_ptr(), out["gc"].data_ptr(),
+                      out["gn"].data_ptr(), loss.data_ptr(), 1, 0.0, stream=s)
+        torch.cuda.synchronize()
+        return out["gc"].cpu().numpy().copy()
+
+    ga = step()
+    tx.copy_(torch.from_numpy(xb))
+    ty.copy_(torch.from_numpy(yb))
+    torch.cuda.synchronize()
+    assert np.array_equal(step(), ga)        # same pointers, no rebind: still the first window
+    ctx.rebind_data()
+    gb = step()
+    ra, rb = O.logp_grad(model, xa, ya, w0), O.logp_grad(model, xb, yb, w0)
+    assert _grad_err(ga, ra["grad"]) < TOL[prec] and _grad_err(gb, rb["grad"]) < TOL[prec]
+    assert _grad_err(gb, ra["grad"]) > 100 * TOL[prec]
+    ctx.close()
+
+
+def test_reset_chain_restarts_the_same_chain(built):
+    """reset_chain drops the captured iteration graph and restarts at w = 0: the same samples again."""
+    m, _ = built
+    rows, n_iter = 3000, 6
+    x, y, _ = m.synth_window(6, 0, rows)
+    for prec in (0, 1):
+        ctx = m.Context(m.baseline_config(precision=prec, sample_capacity=n_iter, seed=11), n_windows=1, rows=rows)
+        ctx.set_window_data(0, x, y)
+        ctx.run_chain(n_iter)
+        first = ctx.get_samples(0).copy()
+        ctx.reset_chain()
+        ctx.run_chain(n_iter)
+        assert np.array_equal(first, ctx.get_samples(0))
+        ctx.close()

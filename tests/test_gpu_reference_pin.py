@@ -3,8 +3,9 @@ kernel, built unmodified from the reference's headers (oracle/ref_harness.cu)
 and run here on the GPU, at the shapes the reference fixes at compile time
 (58368 rows, 22 -> 40 -> 1, Student-t(100, 2.2), N(0, 200^2) prior).
 
-Also writes the captured reference outputs into the run's output folder so that
-they can be committed under tests/golden/ for the CPU-only suite."""
+Also writes the captured reference outputs into $MCMC_B200_GOLDEN_OUT (pytest's
+temporary directory when unset) so that they can be committed under
+tests/golden/ for the CPU-only suite."""
 import ctypes as C
 import os
 
@@ -31,7 +32,7 @@ def _ref_step(ref, x, y, L, eps, w, mom, g):
     return dict(w_next=wn, mom_next=mn, grad_cur=gc, loss_values=loss)
 
 
-def test_oracle_and_cuda_path_against_reference_kernel(built):
+def test_oracle_and_cuda_path_against_reference_kernel(built, tmp_path):
     if not os.path.exists(REF_LIB):
         pytest.skip("reference harness not built (needs the reference tree at build time)")
     m, O = built
@@ -89,7 +90,7 @@ def test_oracle_and_cuda_path_against_reference_kernel(built):
 
     # capture for the CPU-only suite: inputs are regenerated from the seed there,
     # so only small vectors and checksums are stored
-    out_dir = os.path.join(ROOT, "gpurun_out", "golden")
+    out_dir = os.environ.get("MCMC_B200_GOLDEN_OUT") or str(tmp_path)
     os.makedirs(out_dir, exist_ok=True)
     np.savez_compressed(
         os.path.join(out_dir, "reference_ffma_b200.npz"),
