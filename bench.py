@@ -57,7 +57,7 @@ class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
     Q = ("index,clocks.sm,clocks.max.sm,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+         "clocks_event_reasons.sw_power_cap,power.draw")
 
     def __init__(self, device):
         self.device = device
@@ -94,7 +94,7 @@ class ClockSampler:
                 self.lines = [ln.strip() for ln in out.stdout.splitlines() if ln.strip()]
             except Exception:
                 pass
-        sm, mx, reasons = [], [], set()
+        sm, mx, reasons, watts = [], [], set(), []
         for ln in self.lines:
             f = [s.strip() for s in ln.split(",")]
             if len(f) < 8:
@@ -108,9 +108,14 @@ class ClockSampler:
                                f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(name)
+            try:
+                watts.append(float(f[8]))
+            except (IndexError, ValueError):
+                pass
         return {"sm_mhz": float(np.median(sm)) if sm else None,
                 "sm_max_mhz": float(max(mx)) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+                "samples": len(sm), "reasons": sorted(reasons),
+                "power_w": float(np.median(watts)) if watts else None}
 
 
 def host_threads():

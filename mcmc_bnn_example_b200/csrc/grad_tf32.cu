@@ -55,6 +55,7 @@
 #include <cuda.h>
 #include <stdio.h>
 #include <stdlib.h>
+#include <type_traits>
 #include <utility>
 #include "common.cuh"
 #include "chain.cuh"
@@ -99,23 +100,57 @@ struct Tf32Geom {
   static_assert(ES_ATOM_BYTES % 1024 == 0, "E atoms must keep the 1024-byte swizzle alignment");
 };
 
+// Pins a loop-invariant per-thread value in a register: a value that went through a shuffle cannot be
+// recomputed from the thread index at every use (which is what the compiler otherwise does with the
+// address constants of the tile loop when registers are tight, at some 100 instructions per tile).
+__device__ __forceinline__ uint32_t pin(uint32_t v) { return __shfl_sync(0xffffffffu, v, threadIdx.x & 31); }
+
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
   float4 v;
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
   return v;
 }
 
+// E of one pair of hidden units (2J, 2J+1) of this thread's row, stored with the line offsets as immediates
+template <int J>
+__device__ __forceinline__ void store_e_pair(const uint32_t* e_ptr, const uint64_t* hp, uint64_t dy2,
+                                             uint64_t ndy2, uint64_t* dw1p) {
+  const uint64_t h2 = hp[J];
+  const uint64_t t2 = mul2(dy2, h2);
+  dw1p[J] = fma2(dy2, h2, dw1p[J]);
+  float e0, e1;
+  unpack2(fma2(t2, h2, ndy2), e0, e1);
+  asm volatile("st.shared.f32 [%0+%2], %1;" ::"r"(e_ptr[(2 * J) & 7]), "f"(e0), "n"(2 * J * 128) : "memory");
+  asm volatile("st.shared.f32 [%0+%2], %1;" ::"r"(e_ptr[(2 * J + 1) & 7]), "f"(e1), "n"((2 * J + 1) * 128) : "memory");
+}
+template <int... Js>
+__device__ __forceinline__ void store_e_pairs(const uint32_t* e_ptr, const uint64_t* hp, uint64_t dy2,
+                                              uint64_t ndy2, uint64_t* dw1p, std::integer_sequence<int, Js...>) {
+  (store_e_pair<Js>(e_ptr, hp, dy2, ndy2, dw1p), ...);
+}
+
+// Optional per-row loss output as a predicated store (no branch in the tile body)
+__device__ __forceinline__ void store_row_loss(float* base, long long idx, float loss, bool valid) {
+  const uint32_t on = (base != nullptr && valid) ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.f32 [%0], %1;\n\t}" ::"l"(base + idx), "f"(loss),
+      "r"(on)
+      : "memory");
+}
+
 // The slow side of a bounded wait, out of line so that the five waits of a tile cost one test each.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code) {
+// `ok` is false once any wait of this thread has run out: later waits then return at once instead of
+// running out one after the other.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code, bool ok) {
+  if (!ok) return false;
   for (uint32_t i = 0; i < MBAR_WAIT_SLICES; ++i) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   }
   if (status) atomicExch(status, code);
   return false;
 }
-__device__ __forceinline__ bool mbar_wait_q(uint64_t* bar, uint32_t parity, int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  return mbar_wait_slow(bar, parity, status, code);
+__device__ __forceinline__ void mbar_wait_q(uint64_t* bar, uint32_t parity, int* status, int code, bool& ok) {
+  if (!mbar_try_wait(bar, parity)) ok = mbar_wait_slow(bar, parity, status, code, ok);
 }
 
 // One CTA's share of the cross-CTA sum inside a multi-step launch: parameters
@@ -304,23 +339,24 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
     uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
     const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
-    const uint32_t a_t = tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off;
-    const uint32_t z_t = tmem + G::Z_COL0 + wg * G::Z_STRIDE + lane_off;
+    const uint32_t a_t = pin(tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off);
+    const uint32_t z_t = pin(tmem + G::Z_COL0 + wg * G::Z_STRIDE + lane_off);
     // E element (hidden j, row r): atom r/32 (= this warp), line j, 16-byte chunk (r%32)/4 ^ (j%8)
     uint32_t e_ptr[8];
 #pragma unroll
     for (int c = 0; c < 8; ++c)
-      e_ptr[c] = smem_u32(es + wg * G::ES_WG_BYTES + wwarp * G::ES_ATOM_BYTES) +
-                 ((uint32_t)(((lane >> 2) ^ c) << 4)) + ((lane & 3) << 2);
+      e_ptr[c] = pin(smem_u32(es + wg * G::ES_WG_BYTES + wwarp * G::ES_ATOM_BYTES) +
+                     ((uint32_t)(((lane >> 2) ^ c) << 4)) + ((lane & 3) << 2));
     // This thread's row in a staged tile: 32-byte chunk j of row r sits at position j ^ (r % 4).  Rows r
     // and r+4 keep their chunks in the same banks, so the upper four of every eight rows read the two
     // 16-byte halves of a chunk in the opposite order (address ^ 16) and swap them back in registers.
-    const bool swap_halves = (wtid & 4) != 0;
+    const bool swap_halves = pin((uint32_t)(wtid & 4)) != 0;
     const uint32_t xb_wg = smem_u32(xb + wg * NST * G::TILE_BYTES);
     uint32_t x_off[3];
 #pragma unroll
     for (int j = 0; j < 3; ++j)
-      x_off[j] = (uint32_t)(wtid * 128 + ((j ^ (wtid & 3)) << 5) + (swap_halves ? 16 : 0));
+      x_off[j] = pin(xb_wg + (uint32_t)(wtid * 128 + ((j ^ (wtid & 3)) << 5) + ((wtid & 4) ? 16 : 0)));
+    const int row_in_tile = (int)pin((uint32_t)wtid);
     bool alive = true;
 
     for (int it = 0; it < n_iters; ++it) {
@@ -357,14 +393,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       fence_proxy_async_smem();
       __syncthreads();  // S1
 
-      // output-layer weights live in registers for the whole segment, two per register pair
-      uint64_t w1p[H / 2];
-#pragma unroll
-      for (int j = 0; j < H; j += 4) {
-        const float4 v = *reinterpret_cast<const float4*>(w1s + j);
-        w1p[j >> 1] = pack2(v.x, v.y);
-        w1p[(j >> 1) + 1] = pack2(v.z, v.w);
-      }
+      // The output-layer weights are NOT kept in registers: with Z (40), the dW1 accumulators (40) and the
+      // address constants of the tile loop that would leave the compiler the choice between spilling and
+      // recomputing those constants at every use.  They are read from shared memory once per tile instead
+      // (ten 16-byte loads that every lane of the warp shares: one bank cycle each).
+      const uint32_t w1s_addr = smem_u32(w1s);
       const float b1 = b1s;
       uint64_t dw1p[H / 2];  // dW1 accumulators, two hidden units per register pair
 #pragma unroll
@@ -372,97 +405,128 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       float db1 = 0.f;
       double llacc = 0.0;
 
-      // hands this thread's row of the landed tile to the tensor core (forward A operand); returns y
-      auto stage_row = [&]() -> float {
-        const uint32_t stage = st_stage, phase = st_phase;  // of the tile being staged
-        st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
-        st_phase ^= (st_stage == 0) ? 1u : 0u;
-        ok = ok && mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 201);
-        const uint32_t sb = xb_wg + stage * G::TILE_BYTES;
-        float yv = 0.f;
-#pragma unroll
-        for (int j = 0; j < 3; ++j) {
-          const uint32_t a = sb + x_off[j];
-          const float4 p = lds128(a), q = lds128(a ^ 16u);
-          float4 lo, hi;
-          lo.x = swap_halves ? q.x : p.x; lo.y = swap_halves ? q.y : p.y;
-          lo.z = swap_halves ? q.z : p.z; lo.w = swap_halves ? q.w : p.w;
-          hi.x = swap_halves ? p.x : q.x; hi.y = swap_halves ? p.y : q.y;
-          hi.z = swap_halves ? p.z : q.z; hi.w = swap_halves ? p.w : q.w;
-          tc_st8(a_t + j * 8, lo, hi);
-          if (j == 2) yv = hi.w;
-        }
-        return yv;
+      // One 16-byte half-pair of this thread's row of a landed tile: chunk j (features 8j .. 8j+7) goes into
+      // the forward A operand in tensor memory; chunk 2 also carries y.
+      auto stage_load = [&](uint32_t sb, int j, float4& p, float4& q) {
+        const uint32_t a = sb + x_off[j];
+        p = lds128(a);
+        q = lds128(a ^ 16u);
       };
-      // ... and tells the control warp once the stores have landed
+      auto stage_store = [&](int j, const float4& p, const float4& q) -> float {
+        float4 lo, hi;
+        lo.x = swap_halves ? q.x : p.x; lo.y = swap_halves ? q.y : p.y;
+        lo.z = swap_halves ? q.z : p.z; lo.w = swap_halves ? q.w : p.w;
+        hi.x = swap_halves ? p.x : q.x; hi.y = swap_halves ? p.y : q.y;
+        hi.z = swap_halves ? p.z : q.z; hi.w = swap_halves ? p.w : q.w;
+        tc_st8(a_t + j * 8, lo, hi);
+        return hi.w;
+      };
+      // tells the control warp that this thread's row is in tensor memory
       auto publish_row = [&]() {
         tc_wait_st();
         tc_fence_before();
         named_arrive(BAR_ROWS0 + wg, 160);
       };
+      auto next_stage = [&](uint32_t& stage, uint32_t& phase) {
+        stage = st_stage;
+        phase = st_phase;
+        st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
+        st_phase ^= (st_stage == 0) ? 1u : 0u;
+      };
 
       float y = 0.f;
-      if (my_nt > 0) {
-        y = stage_row();
+      if (my_nt > 0) {  // the segment's first tile: nothing to overlap the staging with
+        uint32_t stage, phase;
+        next_stage(stage, phase);
+        mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 201, ok);
+#pragma unroll
+        for (int j = 0; j < 3; ++j) {
+          float4 p, q;
+          stage_load(stage * G::TILE_BYTES, j, p, q);
+          y = stage_store(j, p, q);
+        }
         publish_row();
       }
-      for (int i = 0; i < my_nt; ++i) {
+      // One tile.  HAS_NEXT: the warpgroup has another tile in this segment, whose rows are staged while
+      // this tile's activations are computed (the last tile is the same code without that part, so that the
+      // body has no data-dependent branch the instruction scheduler would have to stop at).
+      auto tile_body = [&](auto has_next_c, int i) {
+        constexpr bool HAS_NEXT = decltype(has_next_c)::value;
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
-        ok = ok && mbar_wait_q(&bar_fwd[wg], n & 1, g.status, 202);
+        // forward(n) done (Z ready, A operand free) and, if there is one, the next tile's rows landed:
+        // both barriers are polled before either answer is used, so their latencies overlap
+        uint32_t stage = 0, phase = 0;
+        if (HAS_NEXT) next_stage(stage, phase);
+        const bool f_done = mbar_try_wait(&bar_fwd[wg], n & 1);
+        const bool t_done = HAS_NEXT ? mbar_try_wait(&bar_tma[wg][stage], phase) : true;
+        if (!f_done) ok = mbar_wait_slow(&bar_fwd[wg], n & 1, g.status, 202, ok);
+        if (HAS_NEXT && !t_done) ok = mbar_wait_slow(&bar_tma[wg][stage], phase, g.status, 201, ok);
         tc_fence_after();
-        // Z(n) starts moving into registers; while it does, forward(n) being done with the A operand, the
-        // next tile's rows go into tensor memory.  The control warp is told only after the tanh pass (the
-        // tensor-memory stores have landed by then): forward(n+1) overwrites the accumulator, which is safe once
-        // Z(n) is in registers, and still has the rest of this tile's epilogue to complete.
+        // Z(n) starts moving into registers.  Once it is there forward(n+1) may overwrite the accumulator;
+        // the control warp is told after the tanh pass, when the next tile's rows are in tensor memory too:
+        // forward(n+1) still has the rest of this tile's epilogue to complete.
         float z[H];
 #pragma unroll
         for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
-        float y_next = 0.f;
-        if (i + 1 < my_nt) y_next = stage_row();
+        const uint32_t sb = stage * G::TILE_BYTES;
+        float4 sp, sq;
+        if (HAS_NEXT) stage_load(sb, 0, sp, sq);
         tc_wait_ld();
+        // hidden activations, kept as register pairs from here on (packed f32x2 arithmetic).  The tanh pass
+        // is bound by the MUFU pipe (one warp instruction per 8 cycles): the staging of the next tile's row
+        // (3 x {two loads, eight selects, one tensor-memory store}) is spread over it.
+        uint64_t hp[H / 2];
         uint64_t pred2 = pack2(b1, 0.f);
+        float y_next = 0.f;
 #pragma unroll
-        for (int j = 0; j < H; j += 2) {
-          z[j] = tanh_fast(z[j]);
-          z[j + 1] = tanh_fast(z[j + 1]);
-          pred2 = fma2(w1p[j >> 1], pack2(z[j], z[j + 1]), pred2);
+        for (int j = 0; j < H; j += 4) {
+          const float4 wv = lds128(w1s_addr + j * 4);
+          hp[j >> 1] = pack2(tanh_fast(z[j]), tanh_fast(z[j + 1]));
+          hp[(j >> 1) + 1] = pack2(tanh_fast(z[j + 2]), tanh_fast(z[j + 3]));
+          pred2 = fma2(pack2(wv.x, wv.y), hp[j >> 1], pred2);
+          pred2 = fma2(pack2(wv.z, wv.w), hp[(j >> 1) + 1], pred2);
+          if (HAS_NEXT) {
+            constexpr int STEP = 12;  // hidden units between two staging steps
+            if (j % STEP == 4) {
+              y_next = stage_store(j / STEP, sp, sq);
+              if (j / STEP < 2) stage_load(sb, j / STEP + 1, sp, sq);
+            }
+          }
         }
         float pred, pred1;
         unpack2(pred2, pred, pred1);
         pred += pred1;
-        if (i + 1 < my_nt) publish_row();
-        const int grow = t * TF32_TILE + wtid;
+        if (HAS_NEXT) publish_row();
+        // the previous tile's backward MMAs must be done with E before it is overwritten (they were
+        // issued a whole tile ago): polled here, used after the loss terms
+        const bool b_done = n > 0 ? mbar_try_wait(&bar_bwd[wg], (n - 1) & 1) : true;
+        const int grow = t * TF32_TILE + row_in_tile;
         const bool valid = grow < g.n_rows;
         float loss, dy;
         lik_terms(g.lik, y, pred, loss, dy);
         if (!valid) { loss = 0.f; dy = 0.f; }
         llacc += (double)loss;
-        if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
+        store_row_loss(g.row_loss, (long long)win * g.row_loss_stride + grow, loss, valid);
         db1 += dy;
+        if (!b_done) ok = mbar_wait_slow(&bar_bwd[wg], (n - 1) & 1, g.status, 203, ok);
         {
           // with t = dy*h:  dW1 += t,  -E = t*h - dy  (E = (1 - h^2) dy; the sign and the W1 factor are
-          // applied once per segment at read-out): three packed operations per pair of hidden units
+          // applied once per segment at read-out): three packed operations per pair of hidden units, each
+          // pair stored as soon as it is ready so that the stores spread over the arithmetic
           const uint64_t dy2 = pack2(dy, dy), ndy2 = pack2(-dy, -dy);
-#pragma unroll
-          for (int j = 0; j < H; j += 2) {
-            const uint64_t h2 = pack2(z[j], z[j + 1]);
-            const uint64_t t2 = mul2(dy2, h2);
-            dw1p[j >> 1] = fma2(dy2, h2, dw1p[j >> 1]);
-            unpack2(fma2(t2, h2, ndy2), z[j], z[j + 1]);
-          }
+          store_e_pairs(e_ptr, hp, dy2, ndy2, dw1p, std::make_integer_sequence<int, H / 2>{});
         }
-        // the previous tile's backward MMAs must be done with E before it is overwritten
-        if (n > 0) ok = ok && mbar_wait_q(&bar_bwd[wg], (n - 1) & 1, g.status, 203);
-        store_e_all(e_ptr, z, std::make_integer_sequence<int, H>{});
         fence_proxy_async_smem();
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
-      }
+      };
+      for (int i = 0; i + 1 < my_nt; ++i) tile_body(std::true_type{}, i);
+      if (my_nt > 0) tile_body(std::false_type{}, my_nt - 1);
       n_done += my_nt;
 
       // ---- this warp's share of dW1 / db1 / log-lik ----
-      if (n_done > 0) ok = ok && mbar_wait_q(&bar_bwd[wg], (n_done - 1) & 1, g.status, 204);
+      if (n_done > 0) mbar_wait_q(&bar_bwd[wg], (n_done - 1) & 1, g.status, 204, ok);
       tc_fence_after();
       {
         // column sums over the warp's 32 rows: a halving butterfly leaves hidden unit `lane` in lane `lane`
