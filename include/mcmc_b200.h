@@ -39,6 +39,9 @@ extern "C" {
 #define MCMC_B200_LIK_STUDENT_T 0    /* global_params.h:39-45 */
 #define MCMC_B200_LIK_GAUSSIAN 1
 
+#define MCMC_B200_RNG_PHILOX 0       /* counter-based, keyed by (seed, global window, iteration): the default */
+#define MCMC_B200_RNG_REFERENCE 1    /* the reference's own streams (main.h:207-216, :235-239), see below */
+
 #define MCMC_B200_PREC_FP32 0        /* FFMA path; stands in for mcmc_step_ffma.h */
 #define MCMC_B200_PREC_TF32 1        /* tcgen05 kind::tf32 path; stands in for mcmc_step_tc.h */
 
@@ -64,6 +67,7 @@ typedef struct mcmc_b200_config {
   int32_t slices;          /* pieces each window is cut into per launch; 0 = chosen from the SM count
                               (fastest).  A fixed value makes a window's results bit-identical
                               however many windows share the context or the GPU. */
+  int32_t rng_streams;     /* MCMC_B200_RNG_*: which random streams drive the chain */
 } mcmc_b200_config;
 
 /* Fills a config with the reference's shipped preset (global_params.h:27-58)
@@ -316,6 +320,26 @@ void mcmc_b200_philox_raw(const uint32_t ctr[4], const uint32_t key[2], uint32_t
  */
 int mcmc_b200_philox_device(mcmc_b200_ctx* ctx, const uint32_t ctr[4], const uint32_t key[2], int n,
                             uint32_t* raw_out, float* normals_out, float* uniform_out);
+
+/*
+ * The reference's random streams (cfg.rng_streams = MCMC_B200_RNG_REFERENCE), for a black-box comparison
+ * with the reference binary.  With rel = 962 * iteration (961 momenta + 1 accept draw per iteration,
+ * main.h:155,216,237):
+ *   momentum p of an iteration : a fresh Thrust default_random_engine (minstd_rand), discard(seed + rel + p),
+ *                                one thrust::normal_distribution<float>(0,1) draw, on the device (main.h:207-216);
+ *   accept draw                : a fresh std::default_random_engine (minstd_rand0) seeded seed + rel + 961, one
+ *                                std::uniform_real_distribution<float>(FLT_MIN, 1) draw, log() in double on
+ *                                the host (main.h:235-239).
+ * Both generators belong to libraries the reference does not pin (Thrust / CCCL, libstdc++); this library
+ * CALLS them (the copies of this toolchain) rather than restating them.  Every window of a context gets the
+ * same streams, as every run of the reference binary does.  The two functions below expose the streams for
+ * tests: the raw engine value after discard(n) / after seed(s), the normal and the log-uniform built on them.
+ * The normal needs a GPU (it is Thrust's device code path that the reference runs); the rest is host code.
+ */
+int mcmc_b200_refstream_momentum_device(mcmc_b200_ctx* ctx, uint64_t first_n, int count, float* out);
+uint32_t mcmc_b200_refstream_engine(uint64_t n_discard);            /* Thrust minstd_rand after discard(n) */
+uint32_t mcmc_b200_refstream_engine0(uint64_t seed);                /* libstdc++ minstd_rand0 seeded, first value */
+float mcmc_b200_refstream_log_uniform(uint64_t seed);               /* log of the accept draw for that seed */
 
 /* Counters for benchmarks: kernels of this library launched on the context
  * since creation (or since the last reset of the counter). */

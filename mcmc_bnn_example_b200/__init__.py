@@ -27,6 +27,7 @@ _HEADERS = ["common.cuh", "chain.cuh", "philox.h", "tc05.cuh"]
 OK = 0
 LIK_STUDENT_T, LIK_GAUSSIAN = 0, 1
 PREC_FP32, PREC_TF32 = 0, 1
+RNG_PHILOX, RNG_REFERENCE = 0, 1
 
 EXPORTS = [
     "mcmc_b200_config_reference", "mcmc_b200_config_baseline", "mcmc_b200_last_error",
@@ -40,7 +41,8 @@ EXPORTS = [
     "mcmc_b200_launch_count", "mcmc_b200_chain_geometry", "mcmc_b200_potential_and_grad_static",
     "mcmc_b200_checkpoint_size", "mcmc_b200_checkpoint_save", "mcmc_b200_checkpoint_load",
     "mcmc_b200_read_table", "mcmc_b200_plan_work_table", "mcmc_b200_rebind_data",
-    "mcmc_b200_selftest_wait_timeout", "mcmc_b200_philox_device",
+    "mcmc_b200_selftest_wait_timeout", "mcmc_b200_philox_device", "mcmc_b200_refstream_momentum_device",
+    "mcmc_b200_refstream_engine", "mcmc_b200_refstream_engine0", "mcmc_b200_refstream_log_uniform",
 ]
 
 
@@ -51,7 +53,7 @@ class Config(C.Structure):
                 ("leapfrog_steps", C.c_int32), ("burn_in", C.c_int32), ("adapt_steps", C.c_int32),
                 ("sample_capacity", C.c_int32), ("eps0", C.c_double), ("target_rate", C.c_double),
                 ("decrement", C.c_double), ("increment", C.c_double), ("seed", C.c_uint64),
-                ("trace_iters", C.c_int32), ("slices", C.c_int32)]
+                ("trace_iters", C.c_int32), ("slices", C.c_int32), ("rng_streams", C.c_int32)]
 
 
 class McmcError(RuntimeError):
@@ -95,6 +97,12 @@ def lib():
         L.mcmc_b200_launch_count.argtypes = [C.c_void_p, C.c_int]
         L.mcmc_b200_philox_normal.restype = C.c_float
         L.mcmc_b200_philox_normal.argtypes = [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32]
+        L.mcmc_b200_refstream_engine.restype = C.c_uint32
+        L.mcmc_b200_refstream_engine.argtypes = [C.c_uint64]
+        L.mcmc_b200_refstream_engine0.restype = C.c_uint32
+        L.mcmc_b200_refstream_engine0.argtypes = [C.c_uint64]
+        L.mcmc_b200_refstream_log_uniform.restype = C.c_float
+        L.mcmc_b200_refstream_log_uniform.argtypes = [C.c_uint64]
         L.mcmc_b200_destroy.argtypes = [C.c_void_p]
         L.mcmc_b200_destroy.restype = None
         _lib = L
@@ -384,6 +392,12 @@ class Context:
         _check(lib().mcmc_b200_philox_device(self._h, c, k, n, raw.ctypes.data_as(C.POINTER(C.c_uint32)),
                                              _fp(nrm), C.byref(u)))
         return raw, nrm, u.value
+
+    def refstream_momentum_device(self, first_n, count):
+        """The reference's momentum stream evaluated on the device: draws first_n .. first_n + count - 1."""
+        out = np.empty(count, np.float32)
+        _check(lib().mcmc_b200_refstream_momentum_device(self._h, C.c_uint64(first_n), count, _fp(out)))
+        return out
 
     def log_acpt(self, prev_loss, new_loss, n_loss, prev_mom, new_mom, grad_cur, eps, stream=None):
         """mcmc::log_acpt_prec on device pointers (ints); returns the host scalar."""

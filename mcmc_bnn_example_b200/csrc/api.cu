@@ -12,8 +12,12 @@
 #include <string.h>
 
 #include <algorithm>
+#include <limits>
+#include <random>
 #include <string>
 #include <vector>
+
+#include <thrust/random.h>
 
 #include "../../include/mcmc_b200.h"
 #include "chain.cuh"
@@ -141,6 +145,9 @@ struct mcmc_b200_ctx {
   bool multistep = false;
   unsigned int* grid_bar = nullptr;
   float* stage = nullptr;  // upload staging for one window: [rows][D] then [rows]
+  // the reference's random streams: host-computed log accept draws, indexed by iteration
+  float* ref_log_u = nullptr;
+  int ref_cap = 0, ref_filled = 0;
   std::vector<void*> allocs;
 };
 
@@ -173,6 +180,7 @@ API void mcmc_b200_config_reference(mcmc_b200_config* cfg) {
   cfg->leapfrog_steps = 1000; cfg->burn_in = 100; cfg->adapt_steps = 100; cfg->sample_capacity = 800;
   cfg->eps0 = 0.01; cfg->target_rate = 0.2; cfg->decrement = 0.1; cfg->increment = 0.01;
   cfg->seed = 0; cfg->trace_iters = 0; cfg->slices = 0;
+  cfg->rng_streams = MCMC_B200_RNG_PHILOX;
 }
 API void mcmc_b200_config_baseline(mcmc_b200_config* cfg) {
   mcmc_b200_config_reference(cfg);
@@ -257,6 +265,8 @@ API int mcmc_b200_create(const mcmc_b200_config* cfg, int device, int n_windows,
     return fail(MCMC_B200_ERR_UNSUPPORTED, "the TF32 path is not built for this hidden width");
   if (cfg->leapfrog_steps < 1 || cfg->lik_scale <= 0 || cfg->prior_scale <= 0)
     return fail(MCMC_B200_ERR_INVALID, "bad sampler/model constants");
+  if (cfg->rng_streams != MCMC_B200_RNG_PHILOX && cfg->rng_streams != MCMC_B200_RNG_REFERENCE)
+    return fail(MCMC_B200_ERR_INVALID, "rng_streams must be MCMC_B200_RNG_PHILOX or MCMC_B200_RNG_REFERENCE");
   if (n_windows > 65535) return fail(MCMC_B200_ERR_INVALID, "at most 65535 windows per context");
   {
     // the kernels index rows of the whole context with 32-bit integers (TMA coordinates, tile numbers)
@@ -649,7 +659,67 @@ static AcceptParams base_accept_params(mcmc_b200_ctx* c) {
   a.Pp = c->Pp;
   a.prior = make_prior(c->cfg);
   a.seed = c->cfg.seed;
+  a.ref_streams = c->cfg.rng_streams == MCMC_B200_RNG_REFERENCE;
+  a.ref_log_u = c->ref_log_u;
+  a.ref_cap = c->ref_cap > 0 ? c->ref_cap : 1;
   return a;
+}
+
+// ---- the reference's random streams (main.h:207-216, :235-239): the libraries' own engines ----------
+constexpr uint64_t REF_DRAWS_PER_ITER = 962;  // 961 momenta + 1 accept draw per iteration (main.h:216,237)
+static float refstream_log_uniform(uint64_t seed) {
+  // main.h:235-239: a fresh engine per draw, U(FLT_MIN, 1), log() evaluated in double and narrowed
+  std::default_random_engine engine;
+  engine.seed((std::default_random_engine::result_type)seed);
+  std::uniform_real_distribution<float> accept_draw(std::numeric_limits<float>::min(), 1.0f);
+  return (float)log((double)accept_draw(engine));
+}
+API uint32_t mcmc_b200_refstream_engine(uint64_t n_discard) {
+  thrust::default_random_engine engine;
+  engine.discard(n_discard);
+  return (uint32_t)engine();
+}
+API uint32_t mcmc_b200_refstream_engine0(uint64_t seed) {
+  std::default_random_engine engine;
+  engine.seed((std::default_random_engine::result_type)seed);
+  return (uint32_t)engine();
+}
+API float mcmc_b200_refstream_log_uniform(uint64_t seed) { return refstream_log_uniform(seed); }
+
+static void drop_graph(mcmc_b200_ctx* c);
+// makes the log accept draws of iterations [0, upto) available on the device (absolute iteration index)
+static int refstream_fill(mcmc_b200_ctx* c, int upto) {
+  if (c->cfg.rng_streams != MCMC_B200_RNG_REFERENCE || upto <= c->ref_filled) return MCMC_B200_OK;
+  if (upto > c->ref_cap) {
+    const int cap = std::max(upto + 64, c->cfg.burn_in + c->cfg.sample_capacity + 64);
+    float* nb = nullptr;
+    int r = dalloc(c, (void**)&nb, (size_t)cap * 4, true);  // (the old buffer stays in the context's free list)
+    if (r) return r;
+    CK(cudaStreamSynchronize(c->stream));
+    c->ref_log_u = nb;
+    c->ref_cap = cap;
+    c->ref_filled = 0;
+    drop_graph(c);  // the captured accept launch holds the old pointer
+  }
+  std::vector<float> h((size_t)(upto - c->ref_filled));
+  for (int it = c->ref_filled; it < upto; ++it)
+    h[(size_t)(it - c->ref_filled)] = refstream_log_uniform(c->cfg.seed + REF_DRAWS_PER_ITER * (uint64_t)it + 961);
+  CK(cudaMemcpyAsync(c->ref_log_u + c->ref_filled, h.data(), h.size() * 4, cudaMemcpyHostToDevice, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  c->ref_filled = upto;
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_refstream_momentum_device(mcmc_b200_ctx* c, uint64_t first_n, int count, float* out) {
+  if (!c || !out || count < 1 || (long long)count > c->rows_pad)
+    return fail(MCMC_B200_ERR_INVALID, "bad arguments (count is limited to the context's padded row count)");
+  CK(cudaSetDevice(c->device));
+  cudaError_t e = launch_refstream_momentum(first_n, count, c->row_loss, c->stream);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  CK(cudaMemcpyAsync(out, c->row_loss, (size_t)count * 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  return MCMC_B200_OK;
 }
 
 static void fill_chain_accept(mcmc_b200_ctx* c, AcceptParams& a, int mode, int L) {
@@ -815,6 +885,10 @@ API int mcmc_b200_run_chain_async(mcmc_b200_ctx* c, int n_iter) {
     if (r) return r;
   }
   if (n_iter == 0) return MCMC_B200_OK;
+  {
+    int r = refstream_fill(c, c->iters_done + n_iter);
+    if (r) return r;
+  }
   // One HMC iteration (L gradient launches + the accept kernel) is captured
   // once and replayed: launch cost stays off the critical path.
   if (!c->graph_tried) {
@@ -916,7 +990,7 @@ struct CkptHeader {
   char magic[8];          // "MCB2CKPT"
   uint32_t version, header_bytes;
   int32_t W, P, Pp, D, H, likelihood, precision, leapfrog_steps, burn_in, adapt_steps, sample_capacity,
-      trace_iters, iters_done, slices;
+      trace_iters, iters_done, slices, rng_streams;
   int64_t rows;
   uint64_t seed;
   uint64_t payload_bytes;
@@ -945,13 +1019,13 @@ CkptHeader ckpt_header(mcmc_b200_ctx* c) {
   CkptHeader h;
   memset(&h, 0, sizeof h);
   memcpy(h.magic, "MCB2CKPT", 8);
-  h.version = 1;
+  h.version = 2;
   h.header_bytes = sizeof(CkptHeader);
   h.W = c->W; h.P = c->P; h.Pp = c->Pp; h.D = c->cfg.D; h.H = c->cfg.H;
   h.likelihood = c->cfg.likelihood; h.precision = c->cfg.precision;
   h.leapfrog_steps = c->cfg.leapfrog_steps; h.burn_in = c->cfg.burn_in; h.adapt_steps = c->cfg.adapt_steps;
   h.sample_capacity = c->cfg.sample_capacity; h.trace_iters = c->cfg.trace_iters;
-  h.iters_done = c->iters_done; h.slices = c->slices;
+  h.iters_done = c->iters_done; h.slices = c->slices; h.rng_streams = c->cfg.rng_streams;
   h.rows = c->rows; h.seed = c->cfg.seed;
   for (const CkptField& f : ckpt_fields(c)) h.payload_bytes += f.bytes;
   return h;
@@ -994,6 +1068,7 @@ API int mcmc_b200_checkpoint_load(mcmc_b200_ctx* c, const void* host_buf, uint64
       h.leapfrog_steps != want.leapfrog_steps || h.burn_in != want.burn_in ||
       h.adapt_steps != want.adapt_steps || h.sample_capacity != want.sample_capacity ||
       h.trace_iters != want.trace_iters || h.rows != want.rows || h.seed != want.seed ||
+      h.rng_streams != want.rng_streams ||
       h.payload_bytes != want.payload_bytes)
     return fail(MCMC_B200_ERR_INVALID, "checkpoint was written by a context with a different configuration");
   if (bytes < sizeof h + h.payload_bytes) return fail(MCMC_B200_ERR_INVALID, "truncated checkpoint");

@@ -12,6 +12,8 @@
 //   * reduce_partials_kernel — row sharding: the vector that is all-reduced.
 //   * predict_kernel, log_acpt_kernel — forward-only pass over stored samples
 //     and the drop-in accept ratio on caller buffers.
+#include <thrust/random.h>
+
 #include "common.cuh"
 #include "chain.cuh"
 #include "philox.h"
@@ -19,6 +21,16 @@
 namespace mcmc_b200 {
 
 constexpr int ACC_THREADS = 256;
+
+// One momentum draw of the reference's stream (main.h:207-213): a fresh Thrust engine advanced by n,
+// one N(0,1) draw.  Thrust's own code does the work, as it does in the reference.
+__device__ __forceinline__ float refstream_normal(unsigned long long n) {
+  thrust::default_random_engine engine;
+  engine.discard(n);
+  thrust::normal_distribution<float> unit_normal(0.f, 1.f);
+  return unit_normal(engine);
+}
+constexpr unsigned long long REF_DRAWS_PER_ITER = 962;  // 961 momenta + 1 accept draw (main.h:216,237)
 
 __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptParams a) {
   __shared__ double dsc[32];
@@ -91,7 +103,8 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
     if (a.mode == ACC_ITERATE) {
       const double la = (ll_new - a.ll_cur[win]) + (lp_new - a.lp_cur[win]) + dk;
       const float la_f = (float)la;
-      const float log_u = logf(philox_accept_uniform(a.seed, gwin, (uint32_t)iter));
+      const float log_u = a.ref_streams ? a.ref_log_u[iter % a.ref_cap]
+                                        : logf(philox_accept_uniform(a.seed, gwin, (uint32_t)iter));
       acc = log_u < la_f;  // main.h:242; a NaN ratio rejects
       if (iter < a.adapt_steps) {  // main.h:266-276
         const float lmr = fminf(la_f, 0.f);
@@ -132,7 +145,9 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
     if (store >= 0 && store < a.sample_capacity)
       a.samples[((size_t)win * a.sample_capacity + store) * a.P + p] = w_state;
     // start of the next iteration: position, fresh momentum (main.h:207-218)
-    const float m = philox_normal(a.seed, gwin, (uint32_t)next_iter, STREAM_MOMENTUM, (uint32_t)p);
+    const float m = a.ref_streams
+                        ? refstream_normal(a.seed + REF_DRAWS_PER_ITER * (unsigned long long)next_iter + p)
+                        : philox_normal(a.seed, gwin, (uint32_t)next_iter, STREAM_MOMENTUM, (uint32_t)p);
     a.w_start[o + p] = w_state;
     a.m_start[o + p] = m;
     a.m0[o + p] = m;
@@ -143,6 +158,15 @@ __global__ void __launch_bounds__(ACC_THREADS) hmc_accept_kernel(const AcceptPar
 
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st) {
   return launch_chain_kernel(hmc_accept_kernel, dim3(windows), dim3(ACC_THREADS), 0, st, a);
+}
+
+__global__ void refstream_momentum_kernel(unsigned long long first_n, int count, float* out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < count) out[i] = refstream_normal(first_n + i);
+}
+cudaError_t launch_refstream_momentum(unsigned long long first_n, int count, float* out, cudaStream_t st) {
+  refstream_momentum_kernel<<<(count + 127) / 128, 128, 0, st>>>(first_n, count, out);
+  return cudaGetLastError();
 }
 
 // ---- bounded-wait self-test ------------------------------------------------

@@ -51,6 +51,10 @@ struct AcceptParams {
   float* prior_loss_out;     // optional [P]
   double* scalars_out;       // [2]: loglik, logprior
   const int* status_in;      // optional: device error word; when it is set the scalars come out as NaN
+  // the reference's random streams instead of Philox (main.h:207-216, :235-239)
+  int ref_streams;
+  const float* ref_log_u;    // [ref_cap] host-computed log accept draws, indexed by iteration % ref_cap
+  int ref_cap;
 };
 
 cudaError_t launch_accept(const AcceptParams& a, int windows, cudaStream_t st);
@@ -63,6 +67,7 @@ cudaError_t launch_predict(int H, const float* xs, long long n, const float* sam
                            float* out, cudaStream_t st);
 cudaError_t launch_philox_probe(const uint32_t ctr[4], const uint32_t key[2], int n, uint32_t* raw, float* normals,
                                 float* uniform, cudaStream_t st);
+cudaError_t launch_refstream_momentum(unsigned long long first_n, int count, float* out, cudaStream_t st);
 cudaError_t launch_wait_probe(int* status, unsigned int slices, cudaStream_t st);
 cudaError_t launch_log_acpt(const float* prev_loss, const float* new_loss, long long n_loss,
                             const float* prev_mom, const float* new_mom, const float* grad_cur, int P,

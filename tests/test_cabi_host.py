@@ -157,3 +157,31 @@ def test_work_partition_covers_every_tile_once_and_is_balanced(slices):
             even_tiles = -(-T // n)
             worst_segments = (even_tiles + tpw - 2) // tpw + 1  # windows an even range can touch
             assert max(costs) <= even_tiles + seg_cost * worst_segments + 1e-9
+
+
+def test_reference_stream_engines_are_the_published_generators():
+    """The reference draws its momenta from Thrust's default engine (minstd_rand, multiplier 48271) and its
+    accept uniforms from libstdc++'s (minstd_rand0, multiplier 16807), both modulo 2^31 - 1 (Park-Miller;
+    the reference's include/mcmc/main.h:207-216, 235-239).  The C++ standard pins the 10000th value of
+    both engines seeded with 1; the library calls the engines themselves, this checks the plumbing
+    around them against a three-line restatement of the recurrence."""
+    import mcmc_bnn_example_b200 as m
+    L = m.lib()
+
+    def lcg(a, x, n):
+        for _ in range(n):
+            x = x * a % 2147483647
+        return x
+
+    assert L.mcmc_b200_refstream_engine(9999) == 399268537      # minstd_rand, [rand.predef]
+    assert lcg(16807, 1, 10000) == 1043618065                   # minstd_rand0, [rand.predef]
+    for n in (0, 1, 961, 962 * 50 + 17, 962 * 900):
+        assert L.mcmc_b200_refstream_engine(n) == lcg(48271, 1, n + 1)
+    for seed in (1, 2, 961, 962 * 7 + 961, 2 ** 31 + 5):
+        s0 = seed % 2147483647 or 1                             # seed 0 (mod m) is mapped to 1
+        x = lcg(16807, s0, 1)
+        assert L.mcmc_b200_refstream_engine0(seed) == x
+        # U(FLT_MIN, 1) from one engine value, log in double, narrowed to float (main.h:235-239)
+        u = (x - 1) / 2147483646.0
+        lu = L.mcmc_b200_refstream_log_uniform(seed)
+        assert abs(lu - np.log(max(u, 1.2e-38))) <= 2e-6 * max(1.0, abs(lu)), (seed, lu, np.log(u))

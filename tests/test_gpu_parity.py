@@ -597,3 +597,48 @@ def test_reset_chain_restarts_the_same_chain(built):
         ctx.run_chain(n_iter)
         assert np.array_equal(first, ctx.get_samples(0))
         ctx.close()
+
+
+@pytest.mark.parametrize("prec", [0, 1])
+def test_reference_random_streams_mode(built, prec):
+    """cfg.rng_streams = RNG_REFERENCE: the chain is driven by the reference's own streams (Thrust minstd_rand
+    + normal_distribution on the device for the momenta, libstdc++ minstd_rand0 + uniform_real_distribution
+    + log on the host for the accept draw, include/mcmc/main.h:207-216, 235-239, with its bookkeeping of 962
+    draws per iteration).  The trace must hold exactly those draws, every window gets the same ones, and
+    the CPU replay with them takes the same decisions."""
+    from scipy.special import ndtr
+    m, O = built
+    rows, n_iter, seed, W = 4096, 14, 5, 2
+    cfg = m.reference_config(precision=prec, leapfrog_steps=10, burn_in=0, adapt_steps=8, sample_capacity=n_iter,
+                             trace_iters=n_iter, seed=seed, eps0=0.2, rng_streams=m.RNG_REFERENCE)
+    ctx = m.Context(cfg, n_windows=W, rows=rows)
+    data = []
+    for w in range(W):
+        x, y, _ = m.synth_window(9, w, rows)
+        data.append((x * np.float32(0.05), y))
+        ctx.set_window_data(w, data[w][0], y, global_window=100 + w)
+    ctx.run_chain(5)
+    ctx.run_chain(n_iter - 5)       # the second call continues the streams where the first stopped
+    L = m.lib()
+    tr = [ctx.get_trace(w) for w in range(W)]
+    assert np.array_equal(tr[0]["momenta"], tr[1]["momenta"]) and np.array_equal(tr[0]["log_u"], tr[1]["log_u"])
+    for it in range(n_iter):
+        dev = ctx.refstream_momentum_device(seed + 962 * it, P)
+        assert np.array_equal(tr[0]["momenta"][it], dev), it
+        assert tr[0]["log_u"][it] == np.float32(L.mcmc_b200_refstream_log_uniform(seed + 962 * it + 961)), it
+    # the normal draw is the inverse normal CDF of ONE engine value: its CDF gives back the engine's
+    # value scaled to (0,1) (or its complement), and the draws are standard normal
+    n0 = 12345
+    v = ctx.refstream_momentum_device(n0, 2000)
+    u = np.array([L.mcmc_b200_refstream_engine(n0 + i) for i in range(2000)], np.float64) / 2147483647.0
+    c = ndtr(v.astype(np.float64))
+    assert min(np.abs(c - u).max(), np.abs(c - (1.0 - u)).max()) < 1e-5
+    big = ctx.refstream_momentum_device(0, 4096)
+    assert abs(big.mean()) < 0.06 and abs(big.std() - 1.0) < 0.05
+    model = O.reference_model(tf32=bool(prec))
+    for w in range(W):
+        ref = O.hmc_chain(model, O.Sampler(10, 8, 0.2, 0.2, 0.1, 0.01), data[w][0], data[w][1], tr[w]["momenta"],
+                          tr[w]["log_u"])
+        clear = np.abs(ref["log_acpt"] - tr[w]["log_u"]) > (0.0 if prec == 0 else 0.05)
+        assert np.array_equal(ref["accepted"][clear], tr[w]["accepted"][clear]), w
+    ctx.close()
