@@ -279,6 +279,19 @@ def run_readme(args, m, torch, dev):
     print(json.dumps(out), flush=True)
 
 
+def run_micro(m, device):
+    """The other roofline denominators, measured here (CUDA events inside the library): L2 read bandwidth at
+    the size of one window and at half the L2, and the MUFU rate for tanh.approx and for the reference's
+    ex2 + rcp pair."""
+    return {
+        "l2_read_gbs_one_window_5p6MB": m.microbench_l2_read(58368 * 96, device),
+        "l2_read_gbs_64MB": m.microbench_l2_read(64 << 20, device),
+        "hbm_read_gbs_2GB": m.microbench_l2_read(2 << 30, device),
+        "mufu_tanh_gvalues_per_s": m.microbench_mufu(0, device),
+        "mufu_ex2_rcp_gvalues_per_s": m.microbench_mufu(1, device),
+    }
+
+
 def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
     """BASELINE configs[1]: one window, TF32, rows sharded 58368/N per GPU, a P+1-double all-reduce
     after every gradient launch.  Latency-bound: expected to get slower with more GPUs."""
@@ -293,6 +306,8 @@ def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
         uid = [m.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         ctx.enable_row_sharding(uid[0], rank, world)
+        if args.allreduce == "oneshot":
+            ctx.enable_oneshot_allreduce()
     ctx.set_window_data(0, x[r0:r1], y[r0:r1], global_window=0)
     stream = torch.cuda.ExternalStream(ctx.stream, device=dev)
     ctx.run_chain(W)
@@ -310,11 +325,12 @@ def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
         dist.barrier()
     ms = e0.elapsed_time(e1)
     launches = ctx.launch_count()
+    ar_us = ctx.time_allreduce(200) if world > 1 else 0.0  # the per-step reduction + all-reduce on its own
     ctx.close()
     if dist is not None:
-        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, ar_us], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t[0])
+        ms, ar_us = float(t[0]), float(t[1])
         dist.destroy_process_group()
     if rank == 0:
         print(json.dumps({
@@ -323,7 +339,9 @@ def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
             "dtype": args.precision, "data": "synthetic",
             "config": {"workload": "BASELINE configs[1]: 1 window x 58368 rows, rows sharded over GPUs, "
                                    "all-reduce of 962 doubles per leapfrog step", "rows_per_gpu": r1 - r0,
-                       "leapfrog_steps": LEAPFROG, "us_per_gradient": 1e3 * ms / (K * LEAPFROG)},
+                       "leapfrog_steps": LEAPFROG, "us_per_gradient": 1e3 * ms / (K * LEAPFROG),
+                       "allreduce": args.allreduce if world > 1 else "none",
+                       "allreduce_us_per_step": ar_us},
             "gpu_launches": launches}), flush=True)
 
 
@@ -336,11 +354,13 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_gpu"])
     ap.add_argument("--windows", type=int, default=WINDOWS, help="total windows over all GPUs")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
-    ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme"],
+    ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme", "micro"],
                     help="windows: configs[2], windows sharded over GPUs (the headline); rows: configs[1], ONE "
                          "window whose rows are sharded, one NCCL all-reduce per leapfrog step")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per window (configs[4]: 1048576)")
     ap.add_argument("--hidden", type=int, default=40, help="hidden units (configs[4]: 128)")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
+                    help="--mode rows: the library's one-shot all-reduce over peer memory, or the NCCL call")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -366,6 +386,10 @@ def main():
     dev = torch.device("cuda", local_rank)
     n_gpus = world
 
+    if args.mode == "micro":
+        if rank == 0:
+            print(json.dumps(run_micro(m, local_rank)), flush=True)
+        return
     if args.mode == "rows":
         return run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev)
     if args.mode == "readme":
@@ -536,6 +560,12 @@ def main():
             "traffic": NCU_DRAM_BYTES_PER_ROW * rows_per_launch,
         },
     }
+    if args.precision == "tf32":
+        # one tanh per hidden unit and row on the MUFU pipe: the second roofline of the TF32 path
+        mufu = m.microbench_mufu(0, local_rank) * 1e9
+        tanh_rate = HID * rows_per_launch / (grad_ms * 1e-3)
+        out["mufu"] = {"tanh_per_s": tanh_rate, "peak_per_s": mufu, "frac": tanh_rate / mufu,
+                       "note": "per GPU; peak measured in this run with tanh.approx.f32 on all SMs"}
     if e2e_ms is not None:
         out["e2e"] = {"value": args.windows * K / (e2e_ms * 1e-3), "unit": UNIT,
                       "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,

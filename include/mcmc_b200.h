@@ -238,6 +238,26 @@ int mcmc_b200_checkpoint_load(mcmc_b200_ctx* ctx, const void* host_buf, uint64_t
 int mcmc_b200_nccl_unique_id(unsigned char id[128]);
 int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* ctx, const unsigned char id[128], int rank,
                                   int nranks);
+/*
+ * Replaces the NCCL call of a row-sharded context (after mcmc_b200_enable_row_sharding, before the chain
+ * starts) by a one-shot all-reduce over peer memory: one launch per leapfrog step sums this rank's
+ * partials, stores them into every rank's receive buffer with plain 8-byte stores over NVLink (buffers
+ * exchanged as CUDA IPC handles over the communicator; every store carries the exchange's sequence number,
+ * so no separate flag or fence is needed), and adds the ranks' contributions in rank order after a
+ * bounded wait, so every rank holds identical bits.  An all-reduce of 7.7 KB is latency, not bandwidth:
+ * this takes a few microseconds where the library call takes about 25 on 8 GPUs.  Needs peer access
+ * between the GPUs (one process per GPU; never two ranks on one GPU: their kernels wait for one another).
+ * A wait that runs out is reported as MCMC_B200_ERR_TIMEOUT by the next synchronising call.
+ */
+int mcmc_b200_enable_oneshot_allreduce(mcmc_b200_ctx* ctx);
+/* Average device time in microseconds of the per-step reduction + all-reduce of a row-sharded context
+ * (whichever of the two is enabled), from CUDA events around `reps` of them on the context's stream.
+ * Collective: every rank calls it with the same reps. */
+int mcmc_b200_time_allreduce(mcmc_b200_ctx* ctx, int reps, float* us_per_call);
+/* Self-test of the one-shot all-reduce's bounded wait on ONE GPU: a fresh one-window context pretends to
+ * be rank 0 of 2, the other rank never sends, the wait runs out after `polls` polls and the call returns
+ * MCMC_B200_ERR_TIMEOUT; the context is an ordinary unsharded one again afterwards. */
+int mcmc_b200_selftest_oneshot_timeout(mcmc_b200_ctx* ctx, int polls);
 
 /*
  * Drop-in for mcmc::mcmc_step<float, L> on caller-owned DEVICE buffers
@@ -340,6 +360,16 @@ int mcmc_b200_refstream_momentum_device(mcmc_b200_ctx* ctx, uint64_t first_n, in
 uint32_t mcmc_b200_refstream_engine(uint64_t n_discard);            /* Thrust minstd_rand after discard(n) */
 uint32_t mcmc_b200_refstream_engine0(uint64_t seed);                /* libstdc++ minstd_rand0 seeded, first value */
 float mcmc_b200_refstream_log_uniform(uint64_t seed);               /* log of the accept draw for that seed */
+
+/*
+ * Device micro-benchmarks behind the roofline figures (no counterpart in the reference): the rate at
+ * which all SMs re-read an L2-resident buffer of `bytes` (one window of the benchmark workload is 5.4 MB
+ * and stays in the L2 between leapfrog steps), and the MUFU pipe's rate for the activation (kind 0:
+ * tanh.approx.f32, one operation per value; kind 1: ex2.approx + rcp.approx, the two operations of the
+ * reference's tanh, kernel_helpers.h:32-44), in 10^9 values per second.  Timed with CUDA events.
+ */
+int mcmc_b200_microbench_l2_read(int device, int64_t bytes, double* gb_per_s);
+int mcmc_b200_microbench_mufu(int device, int kind, double* gvalues_per_s);
 
 /* Counters for benchmarks: kernels of this library launched on the context
  * since creation (or since the last reset of the counter). */

@@ -21,7 +21,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libmcmc_b200.so")
-_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "grad_tf32_wide.cu", "synth.cu", "noalloc.cu", "io.cu"]
+_SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "grad_tf32_wide.cu", "synth.cu", "noalloc.cu", "io.cu",
+            "microbench.cu"]
 _HEADERS = ["common.cuh", "chain.cuh", "philox.h", "tc05.cuh"]
 
 OK = 0
@@ -43,6 +44,8 @@ EXPORTS = [
     "mcmc_b200_read_table", "mcmc_b200_plan_work_table", "mcmc_b200_rebind_data",
     "mcmc_b200_selftest_wait_timeout", "mcmc_b200_philox_device", "mcmc_b200_refstream_momentum_device",
     "mcmc_b200_refstream_engine", "mcmc_b200_refstream_engine0", "mcmc_b200_refstream_log_uniform",
+    "mcmc_b200_microbench_l2_read", "mcmc_b200_microbench_mufu", "mcmc_b200_enable_oneshot_allreduce",
+    "mcmc_b200_time_allreduce", "mcmc_b200_selftest_oneshot_timeout",
 ]
 
 
@@ -165,6 +168,20 @@ def potential_and_grad_static(cfg, x_ptr, y_ptr, rows, w_ptr, grad_ptr, scalars_
     _check(lib().mcmc_b200_potential_and_grad_static(C.byref(cfg), _vp(x_ptr), _vp(y_ptr), C.c_int64(rows),
                                                      _vp(w_ptr), _vp(grad_ptr), _vp(scalars_ptr),
                                                      _vp(stream)))
+
+
+def microbench_l2_read(nbytes, device=0):
+    """GB/s at which all SMs re-read an L2-resident buffer of nbytes (ld.global.cg, 128-bit)."""
+    out = C.c_double()
+    _check(lib().mcmc_b200_microbench_l2_read(device, C.c_int64(nbytes), C.byref(out)))
+    return out.value
+
+
+def microbench_mufu(kind=0, device=0):
+    """10^9 values/s through the MUFU pipe: kind 0 = tanh.approx.f32, kind 1 = ex2.approx + rcp.approx."""
+    out = C.c_double()
+    _check(lib().mcmc_b200_microbench_mufu(device, kind, C.byref(out)))
+    return out.value
 
 
 def read_table(path, rows, total_cols=149, skip_cols=2, D=22, feature_scale=0.001):
@@ -362,6 +379,19 @@ class Context:
     def enable_row_sharding(self, unique_id: bytes, rank, nranks):
         buf = (C.c_ubyte * 128).from_buffer_copy(unique_id)
         _check(lib().mcmc_b200_enable_row_sharding(self._h, buf, rank, nranks))
+
+    def enable_oneshot_allreduce(self):
+        """The per-step all-reduce over peer memory instead of NCCL (after enable_row_sharding)."""
+        _check(lib().mcmc_b200_enable_oneshot_allreduce(self._h))
+
+    def time_allreduce(self, reps=200):
+        us = C.c_float()
+        _check(lib().mcmc_b200_time_allreduce(self._h, reps, C.byref(us)))
+        return us.value
+
+    def selftest_oneshot_timeout(self, polls=2000):
+        code = lib().mcmc_b200_selftest_oneshot_timeout(self._h, int(polls))
+        return code, lib().mcmc_b200_last_error().decode()
 
     # -- drop-ins on device pointers ------------------------------------------
     def mcmc_step(self, x, y, weights_prev, weights_next, mom_prev, mom_next, grad_prev, grad_cur,

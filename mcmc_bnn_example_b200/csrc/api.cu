@@ -57,6 +57,7 @@ struct NcclApi {
   int (*GetUniqueId)(NcclUniqueId*) = nullptr;
   int (*CommInitRank)(NcclComm*, int, NcclUniqueId, int) = nullptr;
   int (*AllReduce)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t) = nullptr;
+  int (*AllGather)(const void*, void*, size_t, int, NcclComm, cudaStream_t) = nullptr;
   int (*CommDestroy)(NcclComm) = nullptr;
   const char* (*GetErrorString)(int) = nullptr;
   bool ok = false;
@@ -80,6 +81,8 @@ bool nccl_load(std::string* why) {
   g_nccl.CommInitRank = (int (*)(NcclComm*, int, NcclUniqueId, int))dlsym(g_nccl.handle, "ncclCommInitRank");
   g_nccl.AllReduce = (int (*)(const void*, void*, size_t, int, int, NcclComm, cudaStream_t))dlsym(
       g_nccl.handle, "ncclAllReduce");
+  g_nccl.AllGather = (int (*)(const void*, void*, size_t, int, NcclComm, cudaStream_t))dlsym(g_nccl.handle,
+                                                                                         "ncclAllGather");
   g_nccl.CommDestroy = (int (*)(NcclComm))dlsym(g_nccl.handle, "ncclCommDestroy");
   g_nccl.GetErrorString = (const char* (*)(int))dlsym(g_nccl.handle, "ncclGetErrorString");
   if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.CommDestroy) {
@@ -90,6 +93,7 @@ bool nccl_load(std::string* why) {
   return true;
 }
 constexpr int kNcclFloat64 = 8;
+constexpr int kNcclChar = 0;
 constexpr int kNcclSum = 0;
 }  // namespace
 
@@ -140,6 +144,13 @@ struct mcmc_b200_ctx {
   // row sharding
   NcclComm comm = nullptr;
   int nranks = 1, rank = 0;
+  // ... with the one-shot all-reduce over peer memory instead of the NCCL call
+  bool oneshot = false;
+  void* os_block = nullptr;                 // this rank's receive buffer + flags (one allocation, IPC-exported)
+  std::vector<void*> os_peer_blocks;        // the peers' blocks as mapped here (null at [rank])
+  std::vector<void*> os_base;               // every rank's block as seen from here (own block at [rank])
+  unsigned int *os_seq = nullptr, *os_done = nullptr;
+  unsigned int os_poll_limit = 1u << 22;    // polls of about 0.1 us .. 1 us each
   long long launches = 0;
   // all L leapfrog steps of an iteration in one cooperative launch (one window, TF32, H = 40)
   bool multistep = false;
@@ -524,6 +535,8 @@ API void mcmc_b200_destroy(mcmc_b200_ctx* c) {
   cudaSetDevice(c->device);
   if (c->stream) cudaStreamSynchronize(c->stream);
   if (c->graph_exec) cudaGraphExecDestroy(c->graph_exec);
+  for (void* p : c->os_peer_blocks)
+    if (p) cudaIpcCloseMemHandle(p);
   if (c->comm && g_nccl.ok) g_nccl.CommDestroy(c->comm);
   for (void* p : c->allocs) cudaFree(p);
   if (c->stream) cudaStreamDestroy(c->stream);
@@ -652,6 +665,34 @@ static int allreduce(mcmc_b200_ctx* c, double* buf, size_t count, cudaStream_t s
   return MCMC_B200_OK;
 }
 
+// this rank's sums and their all-reduce over peer memory in one launch (row sharding, one window)
+static size_t oneshot_block_bytes(const mcmc_b200_ctx* c) {
+  return (size_t)2 * c->nranks * (c->Pp + 4) * 2 * sizeof(uint2);  // [2 halves][nranks][Pp + 4][2 words]
+}
+static int oneshot_allreduce(mcmc_b200_ctx* c, const float* partial, const double* llp, cudaStream_t st) {
+  OneShotParams p;
+  memset(&p, 0, sizeof p);
+  p.partial = partial;
+  p.ll_partial = llp;
+  p.slices = c->slices;
+  p.nslot = c->tab_nslot;
+  p.P = c->P;
+  p.Pp = c->Pp;
+  p.red = c->red;
+  p.rank = c->rank;
+  p.nranks = c->nranks;
+  for (int k = 0; k < c->nranks; ++k) p.peer_words[k] = reinterpret_cast<uint2*>(c->os_base[k]);
+  p.local_words = reinterpret_cast<const uint2*>(c->os_block);
+  p.seq = c->os_seq;
+  p.done = c->os_done;
+  p.poll_limit = c->os_poll_limit;
+  p.status = c->status;
+  cudaError_t e = launch_oneshot_allreduce(p, st);
+  c->launches++;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, std::string("one-shot all-reduce launch: ") + cudaGetErrorString(e));
+  return MCMC_B200_OK;
+}
+
 static AcceptParams base_accept_params(mcmc_b200_ctx* c) {
   AcceptParams a;
   memset(&a, 0, sizeof a);
@@ -729,7 +770,7 @@ static void fill_chain_accept(mcmc_b200_ctx* c, AcceptParams& a, int mode, int L
   const int last = (mode == ACC_BOOTSTRAP) ? 0 : (L - 1) & 1;
   a.partial = c->partial[last];
   a.ll_partial = c->llp[last];
-  a.red_in = (c->comm || c->use_red) ? c->red : nullptr;
+  a.red_in = (c->comm || c->use_red || c->oneshot) ? c->red : nullptr;
   a.w_new = (mode == ACC_BOOTSTRAP) ? c->wbuf[0] : c->wbuf[L & 1];
   a.m_new = (mode == ACC_BOOTSTRAP) ? c->mbuf[0] : c->mbuf[L & 1];
   a.m0 = c->m0;
@@ -768,13 +809,14 @@ static int chain_grad(mcmc_b200_ctx* c, int mode, int s, cudaStream_t st) {
   g.m_out = c->mbuf[(s + 1) & 1];
   g.g_carried = c->g_cur;
   g.partial_in = c->partial[(s + 1) & 1];
-  const bool red = c->comm || c->use_red;
+  const bool red = c->comm || c->use_red || c->oneshot;
   g.red_in = (red && mode == MODE_NEXT) ? c->red : nullptr;
   g.partial_out = c->partial[s & 1];
   g.ll_out = c->llp[s & 1];
   g.eps = c->eps;
   int r = launch_grad(c, g, false, st);
   if (r) return r;
+  if (c->oneshot) return oneshot_allreduce(c, c->partial[s & 1], c->llp[s & 1], st);
   if (red) {
     cudaError_t e = launch_reduce_partials(c->partial[s & 1], c->llp[s & 1], c->slices, c->tab_nslot, c->P,
                                            c->Pp, c->red, c->W, st);
@@ -909,7 +951,7 @@ API int mcmc_b200_run_chain_async(mcmc_b200_ctx* c, int n_iter) {
     c->launches = launches_before;
   }
   const long long per_iter =
-      c->multistep ? 2 : (long long)c->cfg.leapfrog_steps * ((c->comm || c->use_red) ? 2 : 1) + 1;
+      c->multistep ? 2 : (long long)c->cfg.leapfrog_steps * ((c->comm || c->use_red || c->oneshot) ? 2 : 1) + 1;
   for (int i = 0; i < n_iter; ++i) {
     if (c->graph_exec) {
       CK(cudaGraphLaunch(c->graph_exec, c->stream));
@@ -1328,6 +1370,119 @@ API int mcmc_b200_enable_row_sharding(mcmc_b200_ctx* c, const unsigned char id[1
   c->multistep = false;  // every step's sums cross GPUs: one launch + one all-reduce per step
   drop_graph(c);         // a graph captured before this call has neither the sums nor the all-reduce in it
   return MCMC_B200_OK;
+}
+
+// Sets up the peer-memory all-reduce on top of an existing row-sharding communicator: one allocation per
+// rank (receive slots + flags), its CUDA IPC handle gathered over the communicator, every peer's block
+// mapped into this process.  `fake_peers` (self-test only): no communicator, the "peers" are further
+// blocks of THIS GPU that nothing ever writes.
+static int oneshot_setup(mcmc_b200_ctx* c, bool fake_peers) {
+  if (c->nranks > ONESHOT_MAX_RANKS) return fail(MCMC_B200_ERR_INVALID, "too many ranks for the one-shot all-reduce");
+  const size_t block = oneshot_block_bytes(c);
+  int r = dalloc(c, &c->os_block, fake_peers ? block * c->nranks : block, true);
+  if (r) return r;
+  r = dalloc(c, (void**)&c->os_seq, 8, true);
+  if (r) return r;
+  c->os_done = c->os_seq + 1;
+  std::vector<char*> base(c->nranks, nullptr);
+  c->os_peer_blocks.assign(c->nranks, nullptr);
+  if (fake_peers) {
+    for (int k = 0; k < c->nranks; ++k) base[k] = static_cast<char*>(c->os_block) + (size_t)k * block;
+  } else {
+    cudaIpcMemHandle_t mine;
+    CK(cudaIpcGetMemHandle(&mine, c->os_block));
+    char* dh = nullptr;
+    r = dalloc(c, (void**)&dh, sizeof(mine) * c->nranks, true);
+    if (r) return r;
+    CK(cudaMemcpy(dh + sizeof(mine) * c->rank, &mine, sizeof(mine), cudaMemcpyHostToDevice));
+    if (!g_nccl.AllGather) return fail(MCMC_B200_ERR_NCCL, "ncclAllGather missing");
+    int nr = g_nccl.AllGather(dh + sizeof(mine) * c->rank, dh, sizeof(mine), kNcclChar, c->comm, c->stream);
+    if (nr != 0) return fail(MCMC_B200_ERR_NCCL, "ncclAllGather of the IPC handles failed");
+    CK(cudaStreamSynchronize(c->stream));
+    std::vector<cudaIpcMemHandle_t> all(c->nranks);
+    CK(cudaMemcpy(all.data(), dh, sizeof(mine) * c->nranks, cudaMemcpyDeviceToHost));
+    for (int k = 0; k < c->nranks; ++k) {
+      if (k == c->rank) { base[k] = static_cast<char*>(c->os_block); continue; }
+      void* p = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&p, all[k], cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess)
+        return fail(MCMC_B200_ERR_CUDA, std::string("cudaIpcOpenMemHandle (peer access between the GPUs is "
+                                                    "required): ") + cudaGetErrorString(e));
+      c->os_peer_blocks[k] = p;
+      base[k] = static_cast<char*>(p);
+    }
+  }
+  c->os_base.assign(base.begin(), base.end());
+  if (!fake_peers) {
+    // nobody may send before every rank has zeroed and mapped its block: one tiny all-reduce as the barrier
+    int nr = g_nccl.AllReduce(c->red, c->red, 1, kNcclFloat64, kNcclSum, c->comm, c->stream);
+    if (nr != 0) return fail(MCMC_B200_ERR_NCCL, "set-up barrier failed");
+    CK(cudaStreamSynchronize(c->stream));
+  }
+  c->oneshot = true;
+  c->multistep = false;
+  drop_graph(c);
+  return MCMC_B200_OK;
+}
+
+API int mcmc_b200_enable_oneshot_allreduce(mcmc_b200_ctx* c) {
+  if (!c) return fail(MCMC_B200_ERR_INVALID, "null context");
+  if (!c->comm) return fail(MCMC_B200_ERR_INVALID, "call mcmc_b200_enable_row_sharding first");
+  if (c->bootstrapped) return fail(MCMC_B200_ERR_INVALID, "enable it before the chain starts");
+  if (c->oneshot) return MCMC_B200_OK;
+  if (c->W != 1) return fail(MCMC_B200_ERR_INVALID, "row sharding is for contexts with one window");
+  CK(cudaSetDevice(c->device));
+  return oneshot_setup(c, false);
+}
+
+API int mcmc_b200_selftest_oneshot_timeout(mcmc_b200_ctx* c, int polls) {
+  if (!c || polls < 1 || polls > (1 << 24)) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (c->comm || c->oneshot || c->bootstrapped || c->W != 1)
+    return fail(MCMC_B200_ERR_INVALID, "needs a fresh one-window context without row sharding");
+  CK(cudaSetDevice(c->device));
+  // two "ranks" of which only this one ever sends: the wait for the other one must run out
+  c->nranks = 2;
+  c->rank = 0;
+  int r = oneshot_setup(c, true);
+  if (r) return r;
+  c->os_poll_limit = (unsigned int)polls;
+  CK(cudaMemsetAsync(c->partial[0], 0, (size_t)c->slices * c->Pp * 4, c->stream));
+  r = oneshot_allreduce(c, c->partial[0], c->llp[0], c->stream);
+  // back to an unsharded context whatever happened
+  c->oneshot = false;
+  c->nranks = 1;
+  c->os_poll_limit = 1u << 22;
+  drop_graph(c);
+  if (r) return r;
+  return check_status(c);
+}
+
+API int mcmc_b200_time_allreduce(mcmc_b200_ctx* c, int reps, float* us_per_call) {
+  if (!c || reps < 1 || !us_per_call) return fail(MCMC_B200_ERR_INVALID, "bad arguments");
+  if (!c->comm) return fail(MCMC_B200_ERR_INVALID, "row sharding is not enabled");
+  CK(cudaSetDevice(c->device));
+  cudaEvent_t e0, e1;
+  CK(cudaEventCreate(&e0));
+  CK(cudaEventCreate(&e1));
+  auto once = [&]() -> int {
+    if (c->oneshot) return oneshot_allreduce(c, c->partial[0], c->llp[0], c->stream);
+    cudaError_t e = launch_reduce_partials(c->partial[0], c->llp[0], c->slices, c->tab_nslot, c->P, c->Pp, c->red,
+                                           c->W, c->stream);
+    c->launches++;
+    if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+    return allreduce(c, c->red, (size_t)c->W * (c->Pp + 4), c->stream);
+  };
+  for (int i = 0; i < 5; ++i) { int r = once(); if (r) return r; }
+  CK(cudaEventRecord(e0, c->stream));
+  for (int i = 0; i < reps; ++i) { int r = once(); if (r) return r; }
+  CK(cudaEventRecord(e1, c->stream));
+  CK(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  CK(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *us_per_call = 1e3f * ms / reps;
+  return check_status(c);
 }
 
 API int64_t mcmc_b200_launch_count(mcmc_b200_ctx* c, int reset) {

@@ -63,6 +63,28 @@ cudaError_t launch_repack(const float* x, const float* y, float* out, long long 
 cudaError_t launch_reduce_partials(const float* partial, const double* ll_partial, int slices,
                                    const int* nslot, int P, int Pp, double* red, int windows,
                                    cudaStream_t st);
+// One-shot all-reduce over peer memory for row sharding (chain.cu): what every rank's launch needs
+constexpr int ONESHOT_SLICE = 32;   // parameters per CTA
+constexpr int ONESHOT_MAX_RANKS = 16;
+struct OneShotParams {
+  // this rank's partial vectors, as for reduce_partials
+  const float* partial;
+  const double* ll_partial;
+  int slices;
+  const int* nslot;
+  int P, Pp;
+  double* red;                  // [Pp + 4] result, identical bits on every rank
+  int rank, nranks;
+  // every rank's receive buffer (this rank's own at [rank]): [2 halves][nranks][Pp + 4][2] words of
+  // {32 bits of payload, sequence number}
+  uint2* peer_words[ONESHOT_MAX_RANKS];
+  const uint2* local_words;
+  unsigned int* seq;            // device counter of completed exchanges on this rank
+  unsigned int* done;           // ticket of the CTAs of one launch
+  unsigned int poll_limit;      // bounded wait: polls before giving up
+  int* status;
+};
+cudaError_t launch_oneshot_allreduce(const OneShotParams& p, cudaStream_t st);
 cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
                            float* out, cudaStream_t st);
 cudaError_t launch_philox_probe(const uint32_t ctr[4], const uint32_t key[2], int n, uint32_t* raw, float* normals,
