@@ -292,6 +292,33 @@ def run_micro(m, device):
     }
 
 
+def run_predict(args, m, device):
+    """Posterior evaluation after the chain (the reference's output_final_loss, main.h:78-115, and the matching
+    prediction): 800 stored samples of one window against its 58368 rows, through the C-ABI with host
+    buffers.  The work is 800 x 58368 forward passes of 920 FMAs."""
+    S = 800
+    cfg = m.baseline_config(precision=m.PREC_TF32, seed=SEED, sample_capacity=S, leapfrog_steps=LEAPFROG, eps0=EPS)
+    ctx = m.Context(cfg, n_windows=1, rows=ROWS, device=device)
+    x, y, _ = m.synth_window(SEED, 0, ROWS)
+    ctx.set_window_data(0, x, y)
+    ctx.run_chain(S)
+    out = {}
+    for name, fn in (("predict_mean", lambda: ctx.predict_mean(0, x)), ("final_loss", lambda: ctx.final_loss(0))):
+        fn()
+        t0 = time.perf_counter()
+        reps = max(1, args.steps // 20)
+        for _ in range(reps):
+            fn()
+        ms = 1e3 * (time.perf_counter() - t0) / reps
+        fma = S * ROWS * (D * H + H)
+        out[name] = {"ms_per_call": ms, "tfma_per_s": fma / (ms * 1e-3) / 1e12,
+                     "frac_of_fp32_fma_peak": fma / (ms * 1e-3) / (148 * 128 * 1.965e9)}
+    ctx.close()
+    out["config"] = {"workload": "800 stored samples x 58368 rows, 22-40-1, FP32 forward pass, host buffers, "
+                                 "wall clock around the C-ABI call (copies included)"}
+    return out
+
+
 def run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev):
     """BASELINE configs[1]: one window, TF32, rows sharded 58368/N per GPU, a P+1-double all-reduce
     after every gradient launch.  Latency-bound: expected to get slower with more GPUs."""
@@ -354,7 +381,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference", "reference_gpu"])
     ap.add_argument("--windows", type=int, default=WINDOWS, help="total windows over all GPUs")
     ap.add_argument("--precision", default="tf32", choices=["tf32", "fp32"])
-    ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme", "micro"],
+    ap.add_argument("--mode", default="windows", choices=["windows", "rows", "readme", "micro", "predict"],
                     help="windows: configs[2], windows sharded over GPUs (the headline); rows: configs[1], ONE "
                          "window whose rows are sharded, one NCCL all-reduce per leapfrog step")
     ap.add_argument("--rows", type=int, default=ROWS, help="rows per window (configs[4]: 1048576)")
@@ -389,6 +416,10 @@ def main():
     if args.mode == "micro":
         if rank == 0:
             print(json.dumps(run_micro(m, local_rank)), flush=True)
+        return
+    if args.mode == "predict":
+        if rank == 0:
+            print(json.dumps(run_predict(args, m, local_rank)), flush=True)
         return
     if args.mode == "rows":
         return run_row_sharded(args, m, torch, dist, rank, world, local_rank, dev)

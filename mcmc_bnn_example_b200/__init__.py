@@ -22,7 +22,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _ROOT = os.path.dirname(_HERE)
 LIB_PATH = os.path.join(_HERE, "libmcmc_b200.so")
 _SOURCES = ["api.cu", "chain.cu", "grad_fp32.cu", "grad_tf32.cu", "grad_tf32_wide.cu", "synth.cu", "noalloc.cu", "io.cu",
-            "microbench.cu"]
+            "microbench.cu", "forward.cu"]
 _HEADERS = ["common.cuh", "chain.cuh", "philox.h", "tc05.cuh"]
 
 OK = 0

@@ -156,6 +156,11 @@ struct mcmc_b200_ctx {
   bool multistep = false;
   unsigned int* grid_bar = nullptr;
   float* stage = nullptr;  // upload staging for one window: [rows][D] then [rows]
+  // forward-only pass over the stored samples: scratch that grows on demand and is kept (no allocation per call)
+  float* fwd_x = nullptr;
+  float* fwd_out = nullptr;
+  double* fwd_partial = nullptr;
+  size_t fwd_x_cap = 0, fwd_out_cap = 0, fwd_partial_cap = 0;
   // the reference's random streams: host-computed log accept draws, indexed by iteration
   float* ref_log_u = nullptr;
   int ref_cap = 0, ref_filled = 0;
@@ -1295,26 +1300,52 @@ API int mcmc_b200_log_acpt(mcmc_b200_ctx* c, const float* prev_loss, const float
   return MCMC_B200_OK;
 }
 
+// grows a cached scratch buffer (kept for the life of the context; the old one stays in the free list)
+template <typename T>
+static int fwd_reserve(mcmc_b200_ctx* c, T** buf, size_t* cap, size_t need) {
+  if (need <= *cap) return MCMC_B200_OK;
+  T* nb = nullptr;
+  int r = dalloc(c, (void**)&nb, need * sizeof(T), false);
+  if (r) return r;
+  *buf = nb;
+  *cap = need;
+  return MCMC_B200_OK;
+}
+// sample chunks per row tile: enough CTAs for two waves of the GPU, at most one chunk per sample
+static int fwd_chunks(const mcmc_b200_ctx* c, long long n, int count) {
+  const long long tiles = forward_row_tiles(n);
+  long long ch = (2LL * c->num_sms * 3 + tiles - 1) / tiles;
+  ch = std::max<long long>(1, std::min<long long>(std::min<long long>(ch, count), 64));
+  return (int)ch;
+}
+
 API int mcmc_b200_predict_mean(mcmc_b200_ctx* c, int window, const float* xs, int64_t n, int first,
                                int count, float* out) {
   if (!c || !xs || !out || n < 1 || window < 0 || window >= c->W || first < 0 || count < 1 ||
       !c->samples || first + count > c->cfg.sample_capacity)
     return fail(MCMC_B200_ERR_INVALID, "bad arguments or no sample storage");
   CK(cudaSetDevice(c->device));
-  float *dx = nullptr, *dout = nullptr;
-  CK(cudaMalloc(&dx, (size_t)n * c->cfg.D * 4));
-  cudaError_t e = cudaMalloc(&dout, (size_t)n * 4);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(dx, xs, (size_t)n * c->cfg.D * 4, cudaMemcpyHostToDevice, c->stream);
-  if (e == cudaSuccess) {
-    e = launch_predict(c->cfg.H, dx, n, c->samples + ((size_t)window * c->cfg.sample_capacity + first) * c->P,
-                       count, c->P, dout, c->stream);
-    c->launches++;
-  }
-  if (e == cudaSuccess) e = cudaMemcpyAsync(out, dout, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
-  cudaFree(dx);
-  if (dout) cudaFree(dout);
+  const int chunks = fwd_chunks(c, n, count);
+  int r = fwd_reserve(c, &c->fwd_x, &c->fwd_x_cap, (size_t)n * c->cfg.D);
+  if (r == MCMC_B200_OK) r = fwd_reserve(c, &c->fwd_out, &c->fwd_out_cap, (size_t)n);
+  if (r == MCMC_B200_OK) r = fwd_reserve(c, &c->fwd_partial, &c->fwd_partial_cap, (size_t)chunks * n);
+  if (r) return r;
+  CK(cudaMemcpyAsync(c->fwd_x, xs, (size_t)n * c->cfg.D * 4, cudaMemcpyHostToDevice, c->stream));
+  ForwardParams a;
+  memset(&a, 0, sizeof a);
+  a.x = c->fwd_x;
+  a.x_stride = c->cfg.D;
+  a.n = n;
+  a.samples = c->samples + ((size_t)window * c->cfg.sample_capacity + first) * c->P;
+  a.count = count;
+  a.lik = make_lik(c->cfg);
+  a.partial = c->fwd_partial;
+  cudaError_t e = launch_forward_samples(c->cfg.H, a, chunks, false, c->stream);
+  if (e == cudaSuccess) e = launch_forward_finish_predict(c->fwd_partial, chunks, n, count, c->fwd_out, c->stream);
+  c->launches += 2;
   if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  CK(cudaMemcpyAsync(out, c->fwd_out, (size_t)n * 4, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
   return MCMC_B200_OK;
 }
 
@@ -1323,21 +1354,40 @@ API int mcmc_b200_final_loss(mcmc_b200_ctx* c, int window, int first, int count,
   if (!c || window < 0 || window >= c->W || first < 0 || count < 1 || !c->samples ||
       first + count > c->cfg.sample_capacity)
     return fail(MCMC_B200_ERR_INVALID, "bad arguments or no sample storage");
+  if (!c->window_set[window]) return fail(MCMC_B200_ERR_INVALID, "window has no data yet");
   CK(cudaSetDevice(c->device));
-  std::vector<double> sc((size_t)count * 2);
-  double a = 0, b = 0;
-  for (int s = 0; s < count; ++s) {
-    const float* w = c->samples + ((size_t)window * c->cfg.sample_capacity + first + s) * c->P;
-    int r = explicit_steps(c, window, 1, 0.f, w, c->xm[0], c->xg, nullptr, nullptr, c->g_out, nullptr, nullptr,
-                           c->stream, true);
-    if (r) return r;
-    CK(cudaMemcpyAsync(&sc[2 * s], c->scalars, 16, cudaMemcpyDeviceToHost, c->stream));
-  }
-  int r = check_status(c);
+  // all samples against the window's rows in one launch (FP32 forward pass, no gradient)
+  const int tiles = forward_row_tiles(c->rows);
+  const int chunks = fwd_chunks(c, c->rows, count);
+  int r = fwd_reserve(c, &c->fwd_partial, &c->fwd_partial_cap, (size_t)tiles * count + 2 * (size_t)count);
   if (r) return r;
-  for (int s = 0; s < count; ++s) { a += sc[2 * s]; b += sc[2 * s + 1]; }
-  if (mean_loglik) *mean_loglik = a / count;
-  if (mean_logprior) *mean_logprior = b / count;
+  const float* xw = c->xaug + (size_t)window * c->rows_pad * KP;
+  const float* smp = c->samples + ((size_t)window * c->cfg.sample_capacity + first) * c->P;
+  ForwardParams a;
+  memset(&a, 0, sizeof a);
+  a.x = xw;
+  a.x_stride = KP;
+  a.y = xw + COL_Y;
+  a.y_stride = KP;
+  a.n = c->rows;
+  a.samples = smp;
+  a.count = count;
+  a.lik = make_lik(c->cfg);
+  a.partial = c->fwd_partial;
+  double* d_ll = c->fwd_partial + (size_t)tiles * count;
+  double* d_lp = d_ll + count;
+  cudaError_t e = launch_forward_samples(c->cfg.H, a, chunks, true, c->stream);
+  if (e == cudaSuccess)
+    e = launch_forward_finish_loss(c->fwd_partial, tiles, count, smp, c->P, make_prior(c->cfg), d_ll, d_lp, c->stream);
+  c->launches += 2;
+  if (e != cudaSuccess) return fail(MCMC_B200_ERR_CUDA, cudaGetErrorString(e));
+  std::vector<double> h(2 * (size_t)count);
+  CK(cudaMemcpyAsync(h.data(), d_ll, h.size() * 8, cudaMemcpyDeviceToHost, c->stream));
+  CK(cudaStreamSynchronize(c->stream));
+  double sa = 0, sb = 0;
+  for (int s = 0; s < count; ++s) { sa += h[s]; sb += h[count + s]; }  // main.h:100-113: running means
+  if (mean_loglik) *mean_loglik = sa / count;
+  if (mean_logprior) *mean_logprior = sb / count;
   return MCMC_B200_OK;
 }
 

@@ -10,8 +10,7 @@
 //     no host round trip is left inside an iteration.
 //   * repack_kernel — [N][22] + [N] -> [N_pad][24] rows {x, 1, y}.
 //   * reduce_partials_kernel — row sharding: the vector that is all-reduced.
-//   * predict_kernel, log_acpt_kernel — forward-only pass over stored samples
-//     and the drop-in accept ratio on caller buffers.
+//   * log_acpt_kernel — the drop-in accept ratio on caller buffers.
 #include <thrust/random.h>
 
 #include "common.cuh"
@@ -393,46 +392,6 @@ __global__ void __launch_bounds__(RED_PARAMS* RED_GROUPS) oneshot_allreduce_kern
 cudaError_t launch_oneshot_allreduce(const OneShotParams& p, cudaStream_t st) {
   const int n_sl = (p.Pp + 4 + ONESHOT_SLICE - 1) / ONESHOT_SLICE;
   return launch_chain_kernel(oneshot_allreduce_kernel, dim3(n_sl), dim3(RED_PARAMS * RED_GROUPS), 0, st, p);
-}
-
-// ---- posterior-mean prediction -------------------------------------------
-// One thread per row, samples streamed through shared memory; forward pass of
-// mcmc_step_ffma.h:225-281 in FP32 with the reference tanh.
-template <int H>
-__global__ void __launch_bounds__(128) predict_kernel(const float* __restrict__ xs, long long n,
-                                                      const float* __restrict__ samples, int count,
-                                                      int P, float* __restrict__ out) {
-  constexpr int D = 22;
-  extern __shared__ float sw[];  // one sample
-  const long long r = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  float x[D];
-#pragma unroll
-  for (int k = 0; k < D; ++k) x[k] = r < n ? xs[r * D + k] : 0.f;
-  double acc = 0.0;
-  for (int s = 0; s < count; ++s) {
-    __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x) sw[p] = samples[(size_t)s * P + p];
-    __syncthreads();
-    float pred = sw[D * H + 2 * H];
-    for (int j = 0; j < H; ++j) {
-      float z = sw[D * H + j];
-#pragma unroll
-      for (int k = 0; k < D; ++k) z = fmaf(x[k], sw[k * H + j], z);
-      pred = fmaf(sw[D * H + H + j], tanh_ref(z), pred);
-    }
-    acc += (double)pred;
-  }
-  if (r < n) out[r] = (float)(acc / (double)count);
-}
-
-cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
-                           float* out, cudaStream_t st) {
-  const int blocks = (int)((n + 127) / 128);
-  const size_t smem = sizeof(float) * P;
-  if (H == 40) predict_kernel<40><<<blocks, 128, smem, st>>>(xs, n, samples, count, P, out);
-  else if (H == 128) predict_kernel<128><<<blocks, 128, smem, st>>>(xs, n, samples, count, P, out);
-  else return cudaErrorInvalidValue;
-  return cudaGetLastError();
 }
 
 // ---- drop-in accept ratio on caller buffers (kernel_helpers.h:153-188) ----

@@ -85,8 +85,24 @@ struct OneShotParams {
   int* status;
 };
 cudaError_t launch_oneshot_allreduce(const OneShotParams& p, cudaStream_t st);
-cudaError_t launch_predict(int H, const float* xs, long long n, const float* samples, int count, int P,
-                           float* out, cudaStream_t st);
+// forward-only pass over (samples x rows) (forward.cu)
+struct ForwardParams {
+  const float* x;          // rows, x_stride floats apart (22 for caller rows, 24 for the repacked dataset)
+  long long x_stride;
+  const float* y;          // LOSS only: targets, y_stride floats apart
+  long long y_stride;
+  long long n;             // rows
+  const float* samples;    // [count][P]
+  int count;
+  LikParams lik;
+  double* partial;         // PREDICT: [chunks][n]   LOSS: [row tiles][count]
+};
+int forward_row_tiles(long long n);
+cudaError_t launch_forward_samples(int H, const ForwardParams& a, int chunks, bool loss, cudaStream_t st);
+cudaError_t launch_forward_finish_predict(const double* partial, int chunks, long long n, int count, float* out,
+                                          cudaStream_t st);
+cudaError_t launch_forward_finish_loss(const double* partial, int tiles, int count, const float* samples, int P,
+                                       const PriorParams& prior, double* out_ll, double* out_lp, cudaStream_t st);
 cudaError_t launch_philox_probe(const uint32_t ctr[4], const uint32_t key[2], int n, uint32_t* raw, float* normals,
                                 float* uniform, cudaStream_t st);
 cudaError_t launch_refstream_momentum(unsigned long long first_n, int count, float* out, cudaStream_t st);
