@@ -100,17 +100,6 @@ struct Tf32Geom {
   static_assert(ES_ATOM_BYTES % 1024 == 0, "E atoms must keep the 1024-byte swizzle alignment");
 };
 
-// Pins a loop-invariant per-thread value in a register: a value that went through a shuffle cannot be
-// recomputed from the thread index at every use (which is what the compiler otherwise does with the
-// address constants of the tile loop when registers are tight, at some 100 instructions per tile).
-__device__ __forceinline__ uint32_t pin(uint32_t v) { return __shfl_sync(0xffffffffu, v, threadIdx.x & 31); }
-
-__device__ __forceinline__ float4 lds128(uint32_t addr) {
-  float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-  return v;
-}
-
 // E of one pair of hidden units (2J, 2J+1) of this thread's row, stored with the line offsets as immediates
 template <int J>
 __device__ __forceinline__ void store_e_pair(const uint32_t* e_ptr, const uint64_t* hp, uint64_t dy2,
@@ -127,30 +116,6 @@ template <int... Js>
 __device__ __forceinline__ void store_e_pairs(const uint32_t* e_ptr, const uint64_t* hp, uint64_t dy2,
                                               uint64_t ndy2, uint64_t* dw1p, std::integer_sequence<int, Js...>) {
   (store_e_pair<Js>(e_ptr, hp, dy2, ndy2, dw1p), ...);
-}
-
-// Optional per-row loss output as a predicated store (no branch in the tile body)
-__device__ __forceinline__ void store_row_loss(float* base, long long idx, float loss, bool valid) {
-  const uint32_t on = (base != nullptr && valid) ? 1u : 0u;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.f32 [%0], %1;\n\t}" ::"l"(base + idx), "f"(loss),
-      "r"(on)
-      : "memory");
-}
-
-// The slow side of a bounded wait, out of line so that the five waits of a tile cost one test each.
-// `ok` is false once any wait of this thread has run out: later waits then return at once instead of
-// running out one after the other.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code, bool ok) {
-  if (!ok) return false;
-  for (uint32_t i = 0; i < MBAR_WAIT_SLICES; ++i) {
-    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-  }
-  if (status) atomicExch(status, code);
-  return false;
-}
-__device__ __forceinline__ void mbar_wait_q(uint64_t* bar, uint32_t parity, int* status, int code, bool& ok) {
-  if (!mbar_try_wait(bar, parity)) ok = mbar_wait_slow(bar, parity, status, code, ok);
 }
 
 // One CTA's share of the cross-CTA sum inside a multi-step launch: parameters

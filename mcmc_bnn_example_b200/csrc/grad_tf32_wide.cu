@@ -10,11 +10,13 @@
 //     layer, and h written BACK to tensor memory in place of Z.  Then the
 //     per-row loss and dL/dpred.  Pass 2: h again, E = (1 - h^2) dL/dpred to
 //     shared memory, and dW1;
-//   * dW1[j] = sum over rows of dL/dpred * h[j] cannot stay in per-thread
-//     registers either (128 accumulators).  Each warp reduces a 32-column chunk
-//     across its 32 rows with a halving butterfly (31 shuffles: every step a
-//     lane sends one half of its values and keeps the other), which leaves
-//     column `lane` of the chunk in lane `lane`: four accumulators per thread;
+//   * dW1[j] = sum over rows of dL/dpred * h[j]: one accumulator per hidden unit and thread (64 register
+//     pairs, packed fma), kept for a whole segment; the control warpgroup hands its registers to the
+//     compute warpgroups for that (setmaxnreg: 216 / 64).  Once per segment each warp reduces the four
+//     32-column chunks across its 32 rows with a halving butterfly (31 shuffles per chunk: every step a
+//     lane sends one half of its values and keeps the other), which leaves column `lane` of the chunk in
+//     lane `lane`.  (Reducing every tile instead, with four accumulators per thread, cost about 500
+//     instructions per row.)
 //   * E of one tile is 64 KB, so there are two tile pipelines per CTA (two
 //     compute warpgroups + a control warpgroup, 384 threads) with two TMA
 //     stages each, and one Z accumulator per pipeline (2 x 128 columns): the
@@ -35,6 +37,11 @@ namespace mcmc_b200 {
 constexpr int WIDE_NWG = 2;                          // tile pipelines = compute warpgroups
 constexpr int WIDE_THREADS = WIDE_NWG * 128 + 128;   // + a control warpgroup (one warp per pipeline, two idle)
 constexpr int WIDE_NST = 2;                          // TMA stages per pipeline
+// registers: 384 threads start with 168 each; the control warpgroup hands most of its share to the two
+// compute warpgroups (2 * 128 * 216 + 128 * 64 = 63,488 <= 384 * 168), which lets a thread keep one dW1
+// accumulator per hidden unit (128) for a whole segment
+constexpr int WIDE_COMPUTE_REGS = 216;
+constexpr int WIDE_CTRL_REGS = 64;
 
 struct WideGeom {
   // backward N: an M = 128 MMA needs N % 16 == 0, so the whole 32-float staged row (24 real columns +
@@ -131,7 +138,9 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
   const bool is_ctrl = warp >= NCWARPS;
-  const int wg = is_ctrl ? warp - NCWARPS : warp >> 2;  // pipeline this warp computes for / issues for
+  // pipeline this warp computes for / issues for (through a shuffle: visibly the same in every lane, which
+  // keeps the control warps' descriptor arithmetic in uniform registers)
+  const int wg = __shfl_sync(0xffffffffu, is_ctrl ? warp - NCWARPS : warp >> 2, 0);
   const int wtid = tid & 127;         // row of the tile this thread owns
   const int wwarp = warp & 3;         // tensor-memory subpartition of this warp
   const int rows_pad = g.n_tiles * TF32_TILE;
@@ -170,6 +179,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
   //   S1 parameters staged   S2 all tiles of the segment done   S3 read-out done
   if (is_ctrl) {
     // =====================  control warpgroup (one warp per pipeline; the others keep the barriers) ====
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(WIDE_CTRL_REGS));
     uint32_t c_issued = 0;  // tiles of this pipeline whose MMAs have been issued (mbarrier phases follow it)
     for (int sg = seg0; sg < seg1; ++sg) {
       const int4 seg = g.segs[sg];
@@ -231,6 +241,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
       __syncthreads();  // S3
     }
   } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(WIDE_COMPUTE_REGS));
     // =====================  compute warpgroups: one row per thread  =====================================
     uint32_t n_done = 0;  // tiles this pipeline has finished (mbarrier phases follow it)
     uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
@@ -277,9 +288,9 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
       __syncthreads();  // S1
 
       const float b1 = b1s;
-      float dw1acc[NCH];  // lane l: dW1 of hidden unit 32*c + l over this warp's rows
+      uint64_t dw1p[H / 2];  // dW1 of this thread's rows, two hidden units per register pair
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) dw1acc[c] = 0.f;
+      for (int j = 0; j < H / 2; ++j) dw1p[j] = 0ull;
       float db1 = 0.f;
       double llacc = 0.0;
 
@@ -288,7 +299,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
         const uint32_t stage = st_stage, phase = st_phase;
         st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
         st_phase ^= (st_stage == 0) ? 1u : 0u;
-        ok = ok && mbar_wait(&bar_tma[wg][stage], phase, g.status, 301);
+        mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 301, ok);
         // 32-byte chunk j of a row sits at position j ^ (row % 4); rows r and r+4 keep their chunks in
         // the same banks, so the upper four of every eight rows read the two halves in the opposite order
         const unsigned char* xrow = xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128;
@@ -327,7 +338,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
         const bool has_next = i + 1 < my_nt;
-        ok = ok && mbar_wait(&bar_fwd[wg], n & 1, g.status, 302);
+        mbar_wait_q(&bar_fwd[wg], n & 1, g.status, 302, ok);
         tc_fence_after();
         // ---- pass 1: h = tanh(Z) back into tensor memory, output layer ----
         float pred = b1;
@@ -361,10 +372,10 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
         lik_terms(g.lik, y, pred, loss, dy);
         if (!valid) { loss = 0.f; dy = 0.f; }
         llacc += (double)loss;
-        if (g.row_loss && valid) g.row_loss[(long long)win * g.row_loss_stride + grow] = loss;
+        store_row_loss(g.row_loss, (long long)win * g.row_loss_stride + grow, loss, valid);
         db1 += dy;
         // the previous tile's backward MMAs must be done with E before it is overwritten
-        if (n > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n - 1) & 1, g.status, 303);
+        if (n > 0) mbar_wait_q(&bar_bwd[wg], (n - 1) & 1, g.status, 303, ok);
         // ---- pass 2: E to shared memory, dW1 ----
         float y_next = 0.f;
         const float ndy = -dy;
@@ -373,26 +384,24 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
           float v[CH];
           tc_ld32(z_t + c * CH, v);
           tc_wait_ld();
-          if (c == NCH - 1 && has_next) {
-            // Z(n) is in registers everywhere once every thread gets here: the next tile's rows go in
-            // and the control warp may start forward(n+1) while this chunk is finished
-            y_next = stage_row();
-            publish_row();
-          }
-          float e[CH];
           const uint64_t dy2 = pack2(dy, dy), ndy2 = pack2(ndy, ndy);
 #pragma unroll
           for (int j = 0; j < CH; j += 2) {
             const uint64_t h2 = pack2(v[j], v[j + 1]);
+            dw1p[(c * CH + j) >> 1] = fma2(dy2, h2, dw1p[(c * CH + j) >> 1]);
             // (1 - h^2) dy = dy - (h h) dy; the W1 factor is applied at read-out
-            unpack2(fma2(mul2(h2, h2), ndy2, dy2), e[j], e[j + 1]);
-            unpack2(mul2(dy2, h2), v[j], v[j + 1]);
+            unpack2(fma2(mul2(h2, h2), ndy2, dy2), v[j], v[j + 1]);
           }
-          if (c == 0) store_e_wide<0>(e_ptr, e, std::make_integer_sequence<int, CH>{});
-          if (c == 1) store_e_wide<1>(e_ptr, e, std::make_integer_sequence<int, CH>{});
-          if (c == 2) store_e_wide<2>(e_ptr, e, std::make_integer_sequence<int, CH>{});
-          if (c == 3) store_e_wide<3>(e_ptr, e, std::make_integer_sequence<int, CH>{});
-          dw1acc[c] += warp_column_sums(v, lane);
+          if (c == 0) store_e_wide<0>(e_ptr, v, std::make_integer_sequence<int, CH>{});
+          if (c == 1) store_e_wide<1>(e_ptr, v, std::make_integer_sequence<int, CH>{});
+          if (c == 2) store_e_wide<2>(e_ptr, v, std::make_integer_sequence<int, CH>{});
+          if (c == 3) store_e_wide<3>(e_ptr, v, std::make_integer_sequence<int, CH>{});
+        }
+        if (has_next) {
+          // every chunk of h(n) has been read: the next tile's rows go in and the control warp may start
+          // forward(n+1), which overwrites the accumulator
+          y_next = stage_row();
+          publish_row();
         }
         fence_proxy_async_smem();
         named_arrive(BAR_E0 + wg, 160);
@@ -401,10 +410,17 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
       n_done += my_nt;
 
       // ---- this warp's share of dW1 / db1 / log-lik ----
-      if (my_nt > 0) ok = ok && mbar_wait(&bar_bwd[wg], (n_done - 1) & 1, g.status, 304);
+      if (my_nt > 0) mbar_wait_q(&bar_bwd[wg], (n_done - 1) & 1, g.status, 304, ok);
       tc_fence_after();
+      // column sums over the warp's 32 rows, one 32-unit chunk at a time (halving butterfly: lane l ends with
+      // hidden unit 32 c + l), once per segment
 #pragma unroll
-      for (int c = 0; c < NCH; ++c) red_w1[warp][c * CH + lane] = dw1acc[c];
+      for (int c = 0; c < NCH; ++c) {
+        float v[CH];
+#pragma unroll
+        for (int j = 0; j < CH; j += 2) unpack2(dw1p[(c * CH + j) >> 1], v[j], v[j + 1]);
+        red_w1[warp][c * CH + lane] = warp_column_sums(v, lane);
+      }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
         db1 += __shfl_xor_sync(0xffffffffu, db1, o);

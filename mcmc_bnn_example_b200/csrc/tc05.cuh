@@ -113,6 +113,41 @@ __device__ __forceinline__ void store_e_all(const uint32_t* e_ptr, const float* 
   (store_e_one<Js>(e_ptr, z), ...);
 }
 
+// Pins a loop-invariant per-thread value in a register: a value that went through a shuffle cannot be
+// recomputed from the thread index at every use (which is what the compiler otherwise does with the
+// address constants of the tile loop when registers are tight, at some 100 instructions per tile).
+__device__ __forceinline__ uint32_t pin(uint32_t v) { return __shfl_sync(0xffffffffu, v, threadIdx.x & 31); }
+
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
+
+// Optional per-row loss output as a predicated store (no branch in the tile body)
+__device__ __forceinline__ void store_row_loss(float* base, long long idx, float loss, bool valid) {
+  const uint32_t on = (base != nullptr && valid) ? 1u : 0u;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %2, 0;\n\t@p st.global.f32 [%0], %1;\n\t}" ::"l"(base + idx), "f"(loss),
+      "r"(on)
+      : "memory");
+}
+
+// The slow side of a bounded wait, out of line so that the five waits of a tile cost one test each.
+// `ok` is false once any wait of this thread has run out: later waits then return at once instead of
+// running out one after the other.
+static __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, int* status, int code, bool ok) {
+  if (!ok) return false;
+  for (uint32_t i = 0; i < MBAR_WAIT_SLICES; ++i) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+  }
+  if (status) atomicExch(status, code);
+  return false;
+}
+__device__ __forceinline__ void mbar_wait_q(uint64_t* bar, uint32_t parity, int* status, int code, bool& ok) {
+  if (!mbar_try_wait(bar, parity)) ok = mbar_wait_slow(bar, parity, status, code, ok);
+}
+
 // Named hardware barriers hand work from a warpgroup (128 arriving threads) to its control warp
 // (32 waiting threads): a few tens of cycles, no polling.  Ids 1..NWG are the warpgroups' own barriers.
 constexpr int BAR_ROWS0 = 4;   // + wg: rows of a tile are in tensor memory
