@@ -642,3 +642,30 @@ def test_reference_random_streams_mode(built, prec):
         clear = np.abs(ref["log_acpt"] - tr[w]["log_u"]) > (0.0 if prec == 0 else 0.05)
         assert np.array_equal(ref["accepted"][clear], tr[w]["accepted"][clear]), w
     ctx.close()
+
+
+@pytest.mark.parametrize("Hw", [40, 128])
+def test_forward_only_pass_over_samples_ragged_sizes(built, Hw):
+    """predict_mean / final_loss (one forward-only launch over samples x rows) at sizes that are no multiple
+    of its 512-row tiles or of its sample chunks, for both widths, against the oracle's forward pass."""
+    m, O = built
+    rows, n_iter, n_pred = 1531, 7, 777
+    x, y, _ = m.synth_window(12, 0, rows, H=Hw)
+    cfg = m.baseline_config(H=Hw, sample_capacity=n_iter, seed=3, eps0=2e-4)
+    ctx = m.Context(cfg, n_windows=2, rows=rows)
+    ctx.set_window_data(0, x, y, global_window=0)
+    x1, y1, _ = m.synth_window(12, 1, rows, H=Hw)
+    ctx.set_window_data(1, x1, y1, global_window=1)
+    ctx.run_chain(n_iter)
+    model = O.baseline_model(H=Hw)
+    xs, _, _ = m.synth_window(12, 5, n_pred, H=Hw)
+    for w, (xw, yw) in enumerate(((x, y), (x1, y1))):
+        smp = ctx.get_samples(w)
+        for first, count in ((0, n_iter), (2, 3), (6, 1)):
+            got = ctx.predict_mean(w, xs, first, count)
+            exp = O.predict_mean(model, xs, smp[first:first + count])
+            assert np.abs(got - exp).max() <= 1e-5 * max(1.0, np.abs(exp).max()), (w, first, count)
+            ll, lp = ctx.final_loss(w, first, count)
+            ell, elp = O.final_loss(model, xw, yw, smp[first:first + count])
+            assert abs(ll - ell) <= 1e-5 * abs(ell) and abs(lp - elp) <= 1e-5 * max(1.0, abs(elp)), (w, first, count)
+    ctx.close()
