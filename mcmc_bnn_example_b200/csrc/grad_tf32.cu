@@ -486,6 +486,10 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
       };
+      // (unrolled by four: the register copies the compiler places at the loop's back edge — the 20 dW1
+      // pairs and the other values carried from tile to tile — then come once per four tiles: 73 -> 35 move
+      // instructions per row; by eight the loop no longer fits the instruction cache and runs 6 % slower)
+#pragma unroll 4
       for (int i = 0; i + 1 < my_nt; ++i) tile_body(std::true_type{}, i);
       if (my_nt > 0) tile_body(std::false_type{}, my_nt - 1);
       n_done += my_nt;
