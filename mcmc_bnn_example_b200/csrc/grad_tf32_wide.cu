@@ -288,6 +288,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
       __syncthreads();  // S1
 
       const float b1 = b1s;
+      const uint32_t w1s_addr = smem_u32(w1s);
       uint64_t dw1p[H / 2];  // dW1 of this thread's rows, two hidden units per register pair
 #pragma unroll
       for (int j = 0; j < H / 2; ++j) dw1p[j] = 0ull;
@@ -302,13 +303,13 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
         mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 301, ok);
         // 32-byte chunk j of a row sits at position j ^ (row % 4); rows r and r+4 keep their chunks in
         // the same banks, so the upper four of every eight rows read the two halves in the opposite order
-        const unsigned char* xrow = xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128;
+        const uint32_t xrow = smem_u32(xb + (wg * NST + stage) * G::TILE_BYTES + wtid * 128);
         float4 xr[6];
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
-          const unsigned char* cp = xrow + ((j ^ (wtid & 3)) << 5);
-          const float4 first = *reinterpret_cast<const float4*>(cp + (swap_halves ? 16 : 0));
-          const float4 second = *reinterpret_cast<const float4*>(cp + (swap_halves ? 0 : 16));
+          const uint32_t cp = xrow + ((j ^ (wtid & 3)) << 5);
+          const float4 first = lds128(cp + (swap_halves ? 16 : 0));
+          const float4 second = lds128(cp + (swap_halves ? 0 : 16));
           xr[2 * j].x = swap_halves ? second.x : first.x;
           xr[2 * j].y = swap_halves ? second.y : first.y;
           xr[2 * j].z = swap_halves ? second.z : first.z;
@@ -350,7 +351,7 @@ grad_tf32_wide_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradPar
           uint64_t pp0 = 0ull, pp1 = 0ull;  // packed f32x2 accumulators of the output layer
 #pragma unroll
           for (int j = 0; j < CH; j += 4) {
-            const float4 w1v = *reinterpret_cast<const float4*>(w1s + c * CH + j);  // broadcast read
+            const float4 w1v = lds128(w1s_addr + (c * CH + j) * 4);  // broadcast read
             v[j] = tanh_fast(v[j]);
             v[j + 1] = tanh_fast(v[j + 1]);
             v[j + 2] = tanh_fast(v[j + 2]);
