@@ -300,7 +300,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
   } else {
     // =====================  compute warpgroups: one row per thread  =====================================
     asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(TF32_COMPUTE_REGS));
-    const int wg = warp >> 2;
+    // (through a shuffle: visibly the same in every lane, so barrier ids and mbarrier addresses derived from
+    // it stay in uniform registers instead of being recomputed from the thread index at every use)
+    const int wg = __shfl_sync(0xffffffffu, warp >> 2, 0);
     uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
     uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
     const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
