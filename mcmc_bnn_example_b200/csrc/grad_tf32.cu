@@ -246,7 +246,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         const uint64_t wdesc0 = umma_desc_k128(w0s_addr);
         const uint64_t edesc0 = umma_desc_k128(smem_u32(es + wg * G::ES_WG_BYTES));
         const uint64_t xdesc0 = umma_desc_mn32(smem_u32(xb + wg * NST * G::TILE_BYTES), G::GROUP_BYTES);
-        uint32_t stage = c_issued % NST;  // row stage of tile n, kept as a running counter
+        uint32_t stage = 0;  // row stage of tile i of the segment: i % NST, kept as a running counter
         auto issue_fwd = [&]() {
           named_sync(BAR_ROWS0 + wg, 160);
           if (lane == 0) {
@@ -304,7 +304,11 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
     // it stay in uniform registers instead of being recomputed from the thread index at every use)
     const int wg = __shfl_sync(0xffffffffu, warp >> 2, 0);
     uint32_t n_done = 0;  // tiles this warpgroup has finished (mbarrier phases follow it)
-    uint32_t st_stage = 0, st_phase = 0;  // row stage and mbarrier phase of the next tile to be staged
+    // Tile i of a segment (of this warpgroup) uses row stage i % NST, so that the stage is a compile-time
+    // constant in the tile loop (unrolled by NST).  use_s[s] = uses of stage s in earlier segments: the k-th
+    // use of a stage (k from 0) completes the phase of parity k & 1 of its barrier.
+    uint32_t use_s[NST] = {0u, 0u, 0u};
+    static_assert(NST == 3, "the tile loop is unrolled for three row stages");
     const uint32_t lane_off = (uint32_t)(wwarp * 32) << 16;
     const uint32_t a_t = pin(tmem + G::A_COL0 + wg * G::A_STRIDE + lane_off);
     const uint32_t z_t = pin(tmem + G::Z_COL0 + wg * G::Z_STRIDE + lane_off);
@@ -339,9 +343,9 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       if (wtid == 0) {
         for (int i = 0; i < NST && i < my_nt; ++i) {
           const uint32_t n = n_done + i;
-          mbar_expect_tx(&bar_tma[wg][n % NST], G::TILE_BYTES);
-          tma_load_2d(xb + (wg * NST + n % NST) * G::TILE_BYTES, &tmap_mn, 0,
-                      grow0 + (t0 + wg + i * NWG) * TF32_TILE, &bar_tma[wg][n % NST]);
+          mbar_expect_tx(&bar_tma[wg][i], G::TILE_BYTES);
+          tma_load_2d(xb + (wg * NST + i) * G::TILE_BYTES, &tmap_mn, 0,
+                      grow0 + (t0 + wg + i * NWG) * TF32_TILE, &bar_tma[wg][i]);
         }
       }
       // element (n = hidden unit, k) of the K-major B operand at n*128 + ((k/4) ^ (n%8))*16 + (k%4)*4
@@ -394,22 +398,13 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         tc_fence_before();
         named_arrive(BAR_ROWS0 + wg, 160);
       };
-      auto next_stage = [&](uint32_t& stage, uint32_t& phase) {
-        stage = st_stage;
-        phase = st_phase;
-        st_stage = st_stage + 1 == NST ? 0 : st_stage + 1;
-        st_phase ^= (st_stage == 0) ? 1u : 0u;
-      };
-
       float y = 0.f;
       if (my_nt > 0) {  // the segment's first tile: nothing to overlap the staging with
-        uint32_t stage, phase;
-        next_stage(stage, phase);
-        mbar_wait_q(&bar_tma[wg][stage], phase, g.status, 201, ok);
+        mbar_wait_q(&bar_tma[wg][0], use_s[0] & 1, g.status, 201, ok);
 #pragma unroll
         for (int j = 0; j < 3; ++j) {
           float4 p, q;
-          stage_load(stage * G::TILE_BYTES, j, p, q);
+          stage_load(0u, j, p, q);
           y = stage_store(j, p, q);
         }
         publish_row();
@@ -417,18 +412,19 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       // One tile.  HAS_NEXT: the warpgroup has another tile in this segment, whose rows are staged while
       // this tile's activations are computed (the last tile is the same code without that part, so that the
       // body has no data-dependent branch the instruction scheduler would have to stop at).
-      auto tile_body = [&](auto has_next_c, int i) {
+      // NS = row stage of the NEXT tile ((i + 1) % NST), kq = (i + 1) / NST: its use of that stage in this segment
+      auto tile_body = [&](auto has_next_c, auto ns_c, int i, uint32_t kq) {
         constexpr bool HAS_NEXT = decltype(has_next_c)::value;
+        constexpr uint32_t NS = decltype(ns_c)::value;
         const uint32_t n = n_done + i;
         const int t = t0 + wg + i * NWG;
         // forward(n) done (Z ready, A operand free) and, if there is one, the next tile's rows landed:
         // both barriers are polled before either answer is used, so their latencies overlap
-        uint32_t stage = 0, phase = 0;
-        if (HAS_NEXT) next_stage(stage, phase);
+        const uint32_t phase = (use_s[NS] + kq) & 1;
         const bool f_done = mbar_try_wait(&bar_fwd[wg], n & 1);
-        const bool t_done = HAS_NEXT ? mbar_try_wait(&bar_tma[wg][stage], phase) : true;
+        const bool t_done = HAS_NEXT ? mbar_try_wait(&bar_tma[wg][NS], phase) : true;
         if (!f_done) ok = mbar_wait_slow(&bar_fwd[wg], n & 1, g.status, 202, ok);
-        if (HAS_NEXT && !t_done) ok = mbar_wait_slow(&bar_tma[wg][stage], phase, g.status, 201, ok);
+        if (HAS_NEXT && !t_done) ok = mbar_wait_slow(&bar_tma[wg][NS], phase, g.status, 201, ok);
         tc_fence_after();
         // Z(n) starts moving into registers.  Once it is there forward(n+1) may overwrite the accumulator;
         // the control warp is told after the tanh pass, when the next tile's rows are in tensor memory too:
@@ -436,7 +432,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         float z[H];
 #pragma unroll
         for (int c = 0; c < H; c += 8) tc_ld8(z_t + c, z + c);
-        const uint32_t sb = stage * G::TILE_BYTES;
+        constexpr uint32_t sb = NS * G::TILE_BYTES;
         float4 sp, sq;
         if (HAS_NEXT) stage_load(sb, 0, sp, sq);
         tc_wait_ld();
@@ -488,12 +484,24 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         named_arrive(BAR_E0 + wg, 160);
         y = y_next;
       };
-      // (unrolled by four: the register copies the compiler places at the loop's back edge — the 20 dW1
-      // pairs and the other values carried from tile to tile — then come once per four tiles: 73 -> 35 move
-      // instructions per row; by eight the loop no longer fits the instruction cache and runs 6 % slower)
-#pragma unroll 4
-      for (int i = 0; i + 1 < my_nt; ++i) tile_body(std::true_type{}, i);
-      if (my_nt > 0) tile_body(std::false_type{}, my_nt - 1);
+      // The loop is unrolled by the number of row stages, one inlined instance of the body per stage.  (Unrolling
+      // also spreads the register copies the compiler places at the loop's back edge — the 20 dW1 pairs and
+      // the other values carried from tile to tile — over several tiles; unrolled by eight the loop no longer
+      // fits the instruction cache and runs 6 % slower.)
+      {
+        using S0 = std::integral_constant<uint32_t, 0>;
+        using S1 = std::integral_constant<uint32_t, 1>;
+        using S2 = std::integral_constant<uint32_t, 2>;
+        uint32_t k = 0;
+        for (int i = 0; i + 1 < my_nt; i += 3, ++k) {
+          tile_body(std::true_type{}, S1{}, i, k);
+          if (i + 2 < my_nt) tile_body(std::true_type{}, S2{}, i + 1, k);
+          if (i + 3 < my_nt) tile_body(std::true_type{}, S0{}, i + 2, k + 1);
+        }
+        if (my_nt > 0) tile_body(std::false_type{}, S0{}, my_nt - 1, 0u);
+      }
+#pragma unroll
+      for (int st = 0; st < NST; ++st) use_s[st] += (uint32_t)(my_nt - st + NST - 1) / NST;
       n_done += my_nt;
 
       // ---- this warp's share of dW1 / db1 / log-lik ----
