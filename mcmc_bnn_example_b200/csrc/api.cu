@@ -449,7 +449,9 @@ static void plan_work_table(int windows, long long tiles_per_window, int max_cta
     // read-out, worth about `seg_cost` tiles.  A CTA whose range crosses a window boundary therefore
     // gets fewer tiles than one that stays inside a window.  The smallest per-CTA budget that covers
     // all tiles with at most max_ctas CTAs is found by bisection over a greedy walk.
-    const double seg_cost = 8.0;  // measured: 25-window step 0.656 (0) -> 0.621 (6) -> 0.619 ms (9); 200 windows 3.884 -> 3.857
+    // measured with the current kernel (a tile is 0.53 us): 25-window step 0.5135 (8) -> 0.5063 (11) -> 0.5035 ms
+    // (14), flat up to 24; 13 windows 0.284 -> 0.282; 50, 100 and 200 windows unchanged within 0.5 %
+    const double seg_cost = 14.0;
     const long long tpw = tiles_per_window;
     const long long Gmax = std::max<long long>(1, std::min<long long>(max_ctas, T));
     auto walk = [&](double budget_per_cta, bool emit) -> long long {
