@@ -9,9 +9,12 @@
 // Shape of the kernel.  A kernel that allocates tensor memory gets one resident
 // CTA per SM on this toolchain (the occupancy query says 1 whatever its other
 // resources), so the kernel is persistent: one CTA per SM, three compute
-// warpgroups (128 threads = the 128 rows of a tile each) plus one control warp
-// whose lane 0 issues every MMA.  A CTA owns a contiguous range of the launch's
-// (window, tile) list, cut into per-window segments by the host.
+// warpgroups (128 threads = the 128 rows of a tile each) plus a control warpgroup:
+// one warp per compute warpgroup, whose lane 0 issues that warpgroup's MMAs and
+// TMA refills.  A CTA owns a contiguous range of the launch's (window, tile)
+// list, cut into per-window segments by the host; a warpgroup's tiles of a
+// segment use its three row stages round-robin from stage 0, and the tile loop
+// is unrolled by three so that the stage is a compile-time constant.
 //
 //   forward   Z[128 rows x NF] = Xa[128 x 24] . W0a[24 x NF]
 //             Each thread copies ITS row of the staged tile into tensor memory
