@@ -367,11 +367,14 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
       fence_proxy_async_smem();
       __syncthreads();  // S1
 
-      // The output-layer weights are NOT kept in registers: with Z (40), the dW1 accumulators (40) and the
-      // address constants of the tile loop that would leave the compiler the choice between spilling and
-      // recomputing those constants at every use.  They are read from shared memory once per tile instead
-      // (ten 16-byte loads that every lane of the warp shares: one bank cycle each).
-      const uint32_t w1s_addr = smem_u32(w1s);
+      // The output-layer weights are the same for every thread: each is read once per segment and passed
+      // through a shuffle, which tells the compiler that the value is warp-uniform, so that it can keep the 40
+      // of them in uniform registers (63 per warp) next to Z (40 registers) and the dW1 accumulators (40).  Read
+      // from shared memory per tile instead they cost ten 16-byte broadcast loads per row, 160 wavefronts per
+      // tile on the busiest unit of the SM; kept in ordinary registers they cost spills.
+      float w1u[H];
+#pragma unroll
+      for (int j = 0; j < H; ++j) w1u[j] = __shfl_sync(0xffffffffu, w1s[j], 0);
       const float b1 = b1s;
       uint64_t dw1p[H / 2];  // dW1 accumulators, two hidden units per register pair
 #pragma unroll
@@ -447,7 +450,7 @@ grad_tf32_kernel(const __grid_constant__ CUtensorMap tmap_mn, const GradParams g
         float y_next = 0.f;
 #pragma unroll
         for (int j = 0; j < H; j += 4) {
-          const float4 wv = lds128(w1s_addr + j * 4);
+          const float4 wv = make_float4(w1u[j], w1u[j + 1], w1u[j + 2], w1u[j + 3]);
           hp[j >> 1] = pack2(tanh_fast(z[j]), tanh_fast(z[j + 1]));
           hp[(j >> 1) + 1] = pack2(tanh_fast(z[j + 2]), tanh_fast(z[j + 3]));
           pred2 = fma2(pack2(wv.x, wv.y), hp[j >> 1], pred2);
